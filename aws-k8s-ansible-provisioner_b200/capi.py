@@ -6,10 +6,10 @@ import os
 
 # B2_LIB_PATH: an alternative build of the same library (A/B measurements of one source change); never a fallback
 LIB_PATH = os.environ.get("B2_LIB_PATH") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "libb2engine.so")
-ABI_VERSION = 4
-ARCH_QWEN3, ARCH_PHI3, ARCH_OPT, ARCH_LERASUN, ARCH_KEDASUN = 0, 1, 2, 3, 4
-MIXER_LATENT_ATTENTION, MIXER_ATTENTION, MIXER_CONV_ATTENTION = 1, 2, 3
-FF_NONE, FF_ROUTED_EXPERTS, FF_CLAMPED_GATED = 0, 1, 2
+ABI_VERSION = 5
+ARCH_QWEN3, ARCH_PHI3, ARCH_OPT, ARCH_LERASUN, ARCH_KEDASUN, ARCH_BUMALIX = 0, 1, 2, 3, 4, 5
+MIXER_LATENT_ATTENTION, MIXER_ATTENTION, MIXER_CONV_ATTENTION, MIXER_WINDOW_AND_STATE, MIXER_DELTA_STATE = 1, 2, 3, 4, 5
+FF_NONE, FF_ROUTED_EXPERTS, FF_CLAMPED_GATED, FF_POLYNORM, FF_SCALED_GATED_EXPERTS = 0, 1, 2, 3, 4
 NUM_KERNEL_CLASSES = 12
 
 
@@ -24,6 +24,7 @@ class b2_layer_spec(C.Structure):
         ("ff", C.c_int32), ("ff_dim", C.c_int32), ("experts", C.c_int32), ("top", C.c_int32), ("groups", C.c_int32),
         ("groups_keep", C.c_int32), ("kv_heads", C.c_int32), ("conv_taps", C.c_int32), ("window", C.c_int32),
         ("keep_first", C.c_int32), ("v_mix", C.c_int32), ("ff_limit", C.c_float),
+        ("s_heads", C.c_int32), ("s_dim", C.c_int32), ("s_vdim", C.c_int32), ("s_tau", C.c_float), ("shared_ff", C.c_int32),
     ]
 
 
@@ -37,6 +38,7 @@ class b2_config(C.Structure):
         ("arch", C.c_int32), ("rotary_dim", C.c_int32), ("max_positions", C.c_int32), ("sliding_window", C.c_int32),
         ("layer_specs", C.POINTER(b2_layer_spec)), ("compute_f32", C.c_int32), ("logit_scale", C.c_float),
         ("embed_scale", C.c_float), ("norm_groups", C.c_int32),
+        ("loop_start", C.c_int32), ("loop_stop", C.c_int32), ("loop_times", C.c_int32), ("logit_softcap", C.c_float),
     ]
 
 

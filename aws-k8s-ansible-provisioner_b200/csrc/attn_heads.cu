@@ -170,6 +170,43 @@ __global__ void __launch_bounds__(128) heads_finish_kernel(const float* __restri
   }
 }
 
+// Whole-row norms: q (all heads at once) and k (all key heads at once) are each divided by the root mean square of the row and
+// multiplied by a gain per entry; v passes.  One CTA per token.
+template <typename TC>
+__global__ void __launch_bounds__(128) heads_finish_rownorm_kernel(const float* __restrict__ proj, int ld, HeadsGeom g, const float* __restrict__ bias,
+                                                                   const float* __restrict__ qk_gain, const int32_t* __restrict__ slots,
+                                                                   float* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache) {
+  __shared__ float red[2][4];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slot = slots[t];
+  if (slot < 0) return;
+  const int nq = g.heads * g.dim, nk = g.kv_heads * g.dim, nv = g.kv_heads * g.vdim;
+  const float* row = proj + (size_t)t * ld;
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < nq; i += 128) {
+    const float v = row[i] + (bias ? bias[i] : 0.f);
+    sq = fmaf(v, v, sq);
+  }
+  for (int i = threadIdx.x; i < nk; i += 128) {
+    const float v = row[nq + i] + (bias ? bias[nq + i] : 0.f);
+    sk = fmaf(v, v, sk);
+  }
+  sq = warp_sum(sq);
+  sk = warp_sum(sk);
+  if (lane == 0) {
+    red[0][warp] = sq;
+    red[1][warp] = sk;
+  }
+  __syncthreads();
+  const float rq = 1.0f / sqrtf((red[0][0] + red[0][1] + red[0][2] + red[0][3]) / (float)nq + g.eps);
+  const float rk = 1.0f / sqrtf((red[1][0] + red[1][1] + red[1][2] + red[1][3]) / (float)nk + g.eps);
+  for (int i = threadIdx.x; i < nq; i += 128) q_out[(size_t)t * nq + i] = (row[i] + (bias ? bias[i] : 0.f)) * rq * qk_gain[i];
+  for (int i = threadIdx.x; i < nk; i += 128) stf(k_cache + (size_t)slot * nk + i, (row[nq + i] + (bias ? bias[nq + i] : 0.f)) * rk * qk_gain[nq + i]);
+  for (int i = threadIdx.x; i < nv; i += 128) stf(v_cache + (size_t)slot * nv + i, row[nq + nk + i] + (bias ? bias[nq + nk + i] : 0.f));
+}
+
 __global__ void __launch_bounds__(128) conv_tail_store_kernel(const float* __restrict__ proj, int ld, int C, int taps,
                                                               const float* __restrict__ bias, float* __restrict__ ring,
                                                               const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_end,
@@ -728,6 +765,17 @@ int launch_heads_finish(const float* proj, int ld, const HeadsGeom& g, const flo
   }
   if (g.conv_taps > 1)
     B2_CUDA_OK(b2_launch(conv_tail_store_kernel, dim3(T), dim3(128), 0, s, proj, ld, C, g.conv_taps, bias, ring, row_seq, row_end, positions, slots));
+  return 0;
+}
+
+int launch_heads_finish_rownorm(const float* proj, int ld, const HeadsGeom& g, const float* bias, const float* qk_gain, const int32_t* slots,
+                                float* q_out, void* k_cache, void* v_cache, int cache_f32, int T, cudaStream_t s) {
+  if (T <= 0) return 0;
+  B2_REQUIRE(qk_gain != nullptr, "heads_finish_rownorm: the row norms need their gains");
+  if (cache_f32)
+    B2_CUDA_OK(b2_launch(heads_finish_rownorm_kernel<float>, dim3(T), dim3(128), 0, s, proj, ld, g, bias, qk_gain, slots, q_out, (float*)k_cache, (float*)v_cache));
+  else
+    B2_CUDA_OK(b2_launch(heads_finish_rownorm_kernel<bf16>, dim3(T), dim3(128), 0, s, proj, ld, g, bias, qk_gain, slots, q_out, (bf16*)k_cache, (bf16*)v_cache));
   return 0;
 }
 

@@ -1,0 +1,329 @@
+// attn_state.cu -- mixers whose memory is a matrix state per head instead of a cache of keys and values: a head keeps
+// S [dim][vdim] in fp32, every token updates it and reads it out, and the state of a sequence lives in a slot of the
+// engine's sequence table.  Two update rules share the kernels (StateGeom.rule):
+//
+//   STATE_RULE_DECAY   S <- diag(a_t) S + k_t v_t^T;                                  o_t = S^T q_t     (gated linear attention)
+//   STATE_RULE_DELTA   S <- diag(a_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t     (gated delta rule)
+//
+// a_t is a decay per head and key channel in (0, 1); it scales the rows of S.  Query/key head of state head a is
+// a / (heads / kv_heads).
+//
+// Everything here is fp32: the state, the decays (formed as exp(-rate * softplus(.)), never as a power of a rounded
+// sigmoid), the step sizes, the unit norms, the read-out and its norm.  The inputs are the fp32 sums of the fused
+// projection; only the gated read-out handed to the output projection is rounded to the operand type.
+//
+// A step must leave the same state when it is run twice from the same bookkeeping (the eager warm-up ahead of a graph
+// capture): the state of a slot is kept twice, indexed by the parity of the last position it includes.  A portion that
+// starts at position p reads copy (p - 1) & 1 (nothing when p == 0: a sequence starts from zero, so a slot that is
+// used again needs no clearing) and writes copy (p + n - 1) & 1; a decode step therefore never overwrites what it
+// reads.  The convolution keeps its last inputs in a ring of `taps` rows per slot indexed by position mod taps, for the
+// same reason.
+//
+// The scan is sequential in time and parallel over (sequence, head, value column): a CTA owns up to 64 columns of one
+// head's state for one portion, four lanes share a column and split the key channels (channel i * 4 + j belongs to
+// lane j, so the four lanes read consecutive shared-memory words), each lane keeps its channels of the column in
+// registers for the whole portion.  Tokens are staged through shared memory a chunk at a time.  The arithmetic of a token does
+// not depend on where the portion was cut, so prefill, chunked prefill and token-by-token decoding give the same bits.
+//
+// Kernels:
+//   lowrank_act        y = act(W2 . lr + bias) for the low-rank second stages (decays, output gates), fp32
+//   conv_unit_finish   delta rule: causal convolution + silu on q | k | v, unit vectors, query scale, beta
+//   conv_ring_store    the ring update, after every token of the step has read the ring
+//   state_scan         the recurrence
+//   state_out_gate     per-head RMS norm of the read-out with a gain, times the gate (silu or given), operand type out
+#include "kernels.h"
+
+namespace b2 {
+
+namespace {
+
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
+// one warp per output channel group: lr [T][ld] fp32 (rank numbers per token at column lr_off)
+__global__ void __launch_bounds__(256) lowrank_act_kernel(const float* __restrict__ lr, int ld, int lr_off, int rank, const float* __restrict__ w2,
+                                                          const float* __restrict__ bias, const float* __restrict__ rate_log, float rate,
+                                                          int per_head, int mode, float* __restrict__ out, int C) {
+  extern __shared__ float lrs[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < rank; i += 256) lrs[i] = lr[(size_t)t * ld + lr_off + i];
+  __syncthreads();
+  for (int c = blockIdx.y * 256 + threadIdx.x; c < C; c += 256 * gridDim.y) {
+    const float* wr = w2 + (size_t)c * rank;
+    float z = 0.f;
+    for (int r = 0; r < rank; ++r) z = fmaf(wr[r], lrs[r], z);
+    if (bias) z += bias[c];
+    float y;
+    if (mode == LOWRANK_SIGMOID) y = sigmoid_f(z);
+    else if (mode == LOWRANK_DECAY_SIGMOID_POW) y = expf(-rate * softplus_f(-z));              // sigmoid(z)^rate
+    else y = expf(-expf(rate_log[c / per_head]) * softplus_f(z));                              // exp(-exp(A) softplus(z))
+    out[(size_t)t * C + c] = y;
+  }
+}
+
+// One CTA per token, a warp per head unit (query/key heads, then value heads).  proj [T][ld] fp32 = q (kv_heads*dim) | k (kv_heads*dim) |
+// v (heads*vdim) | beta logits (heads) | ...; out [T][C] = the finished q | k | v, beta_out [T][heads].
+__global__ void __launch_bounds__(128) conv_unit_finish_kernel(const float* __restrict__ proj, int ld, StateGeom g, int taps,
+                                                               const float* __restrict__ conv_w, const float* __restrict__ ring,
+                                                               const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_first,
+                                                               const int32_t* __restrict__ positions, const int32_t* __restrict__ slots,
+                                                               float unit_eps, float* __restrict__ out, float* __restrict__ beta_out) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (slots[t] < 0) return;
+  const int pos = positions[t];
+  const int nqk = g.kv_heads * g.dim, nv = g.heads * g.vdim, C = 2 * nqk + nv;
+  const int back = t - row_first[t];
+  const float* row = proj + (size_t)t * ld;
+  const float* rg = ring + (size_t)row_seq[t] * taps * C;
+  float* orow = out + (size_t)t * C;
+  const float qscale = rsqrtf((float)g.dim);
+  const int units = 2 * g.kv_heads + g.heads;
+  for (int u = warp; u < units; u += 4) {
+    const bool is_v = u >= 2 * g.kv_heads;
+    const int width = is_v ? g.vdim : g.dim;
+    const int c0 = is_v ? 2 * nqk + (u - 2 * g.kv_heads) * g.vdim : u * g.dim;
+    float ss = 0.f;
+    for (int i = lane; i < width; i += 32) {
+      const int c = c0 + i;
+      float acc = 0.f;
+      for (int j = 0; j < taps; ++j) {          // y_t = sum_j w[c][j] * x_(t - taps + 1 + j), the last column is the current token's
+        const int d = taps - 1 - j;
+        float xx = 0.f;
+        if (d <= back) xx = (row - (size_t)d * ld)[c];
+        else if (pos - d >= 0) xx = rg[(size_t)((pos - d) % taps) * C + c];
+        acc = fmaf(conv_w[(size_t)c * taps + j], xx, acc);
+      }
+      const float y = silu_f(acc);
+      orow[c] = y;   // (a lane reads back only what it wrote)
+      ss = fmaf(y, y, ss);
+    }
+    if (!is_v) {
+      ss = warp_sum(ss);
+      const float r = (1.0f / sqrtf(ss + unit_eps)) * (u < g.kv_heads ? qscale : 1.0f);
+      for (int i = lane; i < width; i += 32) orow[c0 + i] *= r;
+    }
+  }
+  for (int a = threadIdx.x; a < g.heads; a += 128) beta_out[(size_t)t * g.heads + a] = sigmoid_f(row[C + a]);
+}
+
+__global__ void __launch_bounds__(128) conv_ring_store_kernel(const float* __restrict__ proj, int ld, int C, int taps, float* __restrict__ ring,
+                                                              const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_end,
+                                                              const int32_t* __restrict__ positions, const int32_t* __restrict__ slots) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  if (slots[t] < 0) return;
+  if (row_end[t] - 1 - t >= taps) return;  // a later token of the same portion owns this ring row
+  float* dst = ring + ((size_t)row_seq[t] * taps + positions[t] % taps) * C;
+  const float* row = proj + (size_t)t * ld;
+  for (int c = threadIdx.x; c < C; c += 128) dst[c] = row[c];
+}
+
+constexpr int SC_LANES = 4;     // lanes that share a state column
+constexpr int SC_COLS = 64;     // columns of a CTA at most
+constexpr int SC_CHUNK = 16;    // tokens staged at a time
+
+// grid (portions, heads, column tiles); block cols * 4.  DPT = key channels per lane (dim <= 4 * DPT).
+template <int DPT, int RULE>
+__global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
+                                                                       const float* __restrict__ v, int ldv, const float* __restrict__ decay,
+                                                                       const float* __restrict__ beta, StateGeom g, float qscale,
+                                                                       float* __restrict__ state, const int32_t* __restrict__ last_rows,
+                                                                       const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_first,
+                                                                       const int32_t* __restrict__ row_end, const int32_t* __restrict__ positions,
+                                                                       const int32_t* __restrict__ slots, float* __restrict__ out, int cols) {
+  constexpr int DP = DPT * SC_LANES;
+  constexpr int CH = DPT >= 64 ? SC_CHUNK / 2 : SC_CHUNK;   // (static shared memory ends at 48 KB)
+  __shared__ __align__(16) float qs[CH][DP], ks[CH][DP], as[CH][DP];
+  __shared__ float vs[CH][SC_COLS], bs[CH];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r_last = last_rows ? last_rows[blockIdx.x] : (int)blockIdx.x;
+  const int first = row_first[r_last], end = row_end[r_last];
+  if (slots[first] < 0) return;   // padding row of a decode bucket
+  const int a = blockIdx.y, kh = a / (g.heads / g.kv_heads);
+  const int col0 = blockIdx.z * cols;
+  const int ci = threadIdx.x / SC_LANES, j = threadIdx.x % SC_LANES;
+  const int col = col0 + ci;
+  const bool live = col < g.vdim;
+  const int pos0 = positions[first], n = end - first;
+  const size_t head_floats = (size_t)g.dim * g.vdim;
+  float* sbase = state + ((size_t)row_seq[first] * 2 * g.heads) * head_floats;
+  const float* s_in = sbase + ((size_t)((pos0 + 1) & 1) * g.heads + a) * head_floats;
+  float* s_out = sbase + ((size_t)((pos0 + n - 1) & 1) * g.heads + a) * head_floats;
+  float s[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) {
+    const int d = i * SC_LANES + j;
+    s[i] = (pos0 > 0 && live && d < g.dim) ? s_in[(size_t)d * g.vdim + col] : 0.f;
+  }
+  const int nthreads = blockDim.x;
+  for (int c0 = 0; c0 < n; c0 += CH) {
+    const int cn = min(CH, n - c0);
+    __syncthreads();   // the chunk before this one has been consumed
+    for (int i = threadIdx.x; i < cn * DP; i += nthreads) {
+      const int tt = i / DP, d = i % DP;
+      const size_t row = (size_t)(first + c0 + tt);
+      const bool in = d < g.dim;
+      qs[tt][d] = in ? q[row * ldq + kh * g.dim + d] * qscale : 0.f;
+      ks[tt][d] = in ? k[row * ldk + kh * g.dim + d] : 0.f;
+      as[tt][d] = in ? decay[row * ((size_t)g.heads * g.dim) + a * g.dim + d] : 1.f;
+    }
+    for (int i = threadIdx.x; i < cn * cols; i += nthreads) {
+      const int tt = i / cols, c = i % cols;
+      vs[tt][c] = col0 + c < g.vdim ? v[(size_t)(first + c0 + tt) * ldv + a * g.vdim + col0 + c] : 0.f;
+    }
+    if (RULE == STATE_RULE_DELTA)
+      for (int i = threadIdx.x; i < cn; i += nthreads) bs[i] = beta[(size_t)(first + c0 + i) * g.heads + a];
+    __syncthreads();
+    for (int tt = 0; tt < cn; ++tt) {
+      const float vc = vs[tt][ci];
+      float acc = 0.f;
+      if (RULE == STATE_RULE_DECAY) {
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+          const int d = i * SC_LANES + j;
+          s[i] = fmaf(as[tt][d], s[i], ks[tt][d] * vc);
+          acc = fmaf(s[i], qs[tt][d], acc);
+        }
+      } else {
+        float kv = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+          const int d = i * SC_LANES + j;
+          s[i] *= as[tt][d];
+          kv = fmaf(s[i], ks[tt][d], kv);
+        }
+        kv += __shfl_xor_sync(0xffffffffu, kv, 1);
+        kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+        const float u = bs[tt] * (vc - kv);
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+          const int d = i * SC_LANES + j;
+          s[i] = fmaf(ks[tt][d], u, s[i]);
+          acc = fmaf(s[i], qs[tt][d], acc);
+        }
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      if (j == 0 && live) out[(size_t)(first + c0 + tt) * ((size_t)g.heads * g.vdim) + a * g.vdim + col] = acc;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+      const int d = i * SC_LANES + j;
+      if (d < g.dim) s_out[(size_t)d * g.vdim + col] = s[i];
+    }
+  }
+}
+
+// One warp per (token, head): y = o / sqrt(mean(o^2) + eps) * gain * gate, gate = silu(gate_in) or gate_in as it is.
+template <typename TX>
+__global__ void __launch_bounds__(128) state_out_gate_kernel(const float* __restrict__ o, const float* __restrict__ gain,
+                                                             const float* __restrict__ gate, int gate_ld, int gate_silu, TX* __restrict__ out,
+                                                             int heads, int vdim, float eps, int T) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long unit = (long)blockIdx.x * 4 + warp;
+  if (unit >= (long)T * heads) return;
+  const int t = (int)(unit / heads), a = (int)(unit % heads);
+  const float* orow = o + ((size_t)t * heads + a) * vdim;
+  const float* grow = gate + (size_t)t * gate_ld + (size_t)a * vdim;
+  float ss = 0.f;
+  for (int i = lane; i < vdim; i += 32) ss = fmaf(orow[i], orow[i], ss);
+  ss = warp_sum(ss);
+  const float r = 1.0f / sqrtf(ss / (float)vdim + eps);
+  TX* dst = out + ((size_t)t * heads + a) * vdim;
+  for (int i = lane; i < vdim; i += 32) {
+    const float gt = gate_silu ? silu_f(grow[i]) : grow[i];
+    dst[i] = (TX)(orow[i] * r * gain[i] * gt);
+  }
+}
+
+template <int RULE>
+int launch_scan_rule(int dpt, dim3 grid, dim3 block, cudaStream_t s, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
+                     const float* decay, const float* beta, const StateGeom& g, float qscale, float* state, const int32_t* last_rows,
+                     const int32_t* row_seq, const int32_t* row_first, const int32_t* row_end, const int32_t* positions, const int32_t* slots,
+                     float* out, int cols) {
+#define B2_SCAN_CASE(D)                                                                                                                    \
+  case D:                                                                                                                                  \
+    B2_CUDA_OK(b2_launch(state_scan_kernel<D, RULE>, grid, block, 0, s, q, ldq, k, ldk, v, ldv, decay, beta, g, qscale, state, last_rows,  \
+                         row_seq, row_first, row_end, positions, slots, out, cols));                                                       \
+    return 0;
+  switch (dpt) {
+    B2_SCAN_CASE(2)
+    B2_SCAN_CASE(4)
+    B2_SCAN_CASE(8)
+    B2_SCAN_CASE(16)
+    B2_SCAN_CASE(32)
+    B2_SCAN_CASE(64)
+  }
+#undef B2_SCAN_CASE
+  b2_set_error("state_scan: key width %d not built (at most 256)", g.dim);
+  return -22;
+}
+
+}  // namespace
+
+int launch_lowrank_act(const float* lr, int ld, int lr_off, int rank, const float* w2, const float* bias, int mode, float rate,
+                       const float* rate_log, int per_head, float* out, int T, int C, cudaStream_t s) {
+  if (T <= 0 || C <= 0) return 0;
+  B2_REQUIRE(rank >= 1 && rank <= 8192, "lowrank_act: rank %d", rank);
+  B2_REQUIRE(mode != LOWRANK_DECAY_SOFTPLUS || (rate_log != nullptr && per_head >= 1), "lowrank_act: the softplus decay needs a rate per head");
+  const dim3 grid(T, T >= 512 ? 1 : std::max(1, std::min((C + 255) / 256, 512 / T)));
+  B2_CUDA_OK(b2_launch(lowrank_act_kernel, grid, dim3(256), (size_t)rank * 4, s, lr, ld, lr_off, rank, w2, bias, rate_log, rate,
+                       per_head > 0 ? per_head : 1, mode, out, C));
+  return 0;
+}
+
+int launch_conv_unit_finish(const float* proj, int ld, const StateGeom& g, int taps, const float* conv_w, float* ring, const int32_t* row_seq,
+                            const int32_t* row_first, const int32_t* row_end, const int32_t* positions, const int32_t* slots, float unit_eps,
+                            float* out, float* beta_out, int T, cudaStream_t s) {
+  if (T <= 0) return 0;
+  B2_REQUIRE(taps >= 1 && conv_w && ring && row_seq && row_first && row_end, "conv_unit_finish: the convolution needs its weights and state");
+  const int C = 2 * g.kv_heads * g.dim + g.heads * g.vdim;
+  B2_CUDA_OK(b2_launch(conv_unit_finish_kernel, dim3(T), dim3(128), 0, s, proj, ld, g, taps, conv_w, (const float*)ring, row_seq, row_first,
+                       positions, slots, unit_eps, out, beta_out));
+  if (taps > 1)
+    B2_CUDA_OK(b2_launch(conv_ring_store_kernel, dim3(T), dim3(128), 0, s, proj, ld, C, taps, ring, row_seq, row_end, positions, slots));
+  return 0;
+}
+
+int launch_state_scan(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* decay, const float* beta,
+                      const StateGeom& g, float qscale, float* state, int portions, const int32_t* last_rows, const int32_t* row_seq,
+                      const int32_t* row_first, const int32_t* row_end, const int32_t* positions, const int32_t* slots, float* out,
+                      cudaStream_t s) {
+  if (portions <= 0) return 0;
+  B2_REQUIRE(g.heads >= 1 && g.kv_heads >= 1 && g.heads % g.kv_heads == 0 && g.dim >= 1 && g.vdim >= 1, "state_scan: bad sizes");
+  B2_REQUIRE(g.rule == STATE_RULE_DECAY || (g.rule == STATE_RULE_DELTA && beta != nullptr), "state_scan: rule %d", g.rule);
+  int dpt = 2;
+  while (dpt * SC_LANES < g.dim) dpt *= 2;
+  const int cols = std::min(SC_COLS, (g.vdim + 7) / 8 * 8);
+  const dim3 grid(portions, g.heads, (g.vdim + cols - 1) / cols), block(cols * SC_LANES);
+  if (g.rule == STATE_RULE_DECAY)
+    return launch_scan_rule<STATE_RULE_DECAY>(dpt, grid, block, s, q, ldq, k, ldk, v, ldv, decay, beta, g, qscale, state, last_rows, row_seq,
+                                              row_first, row_end, positions, slots, out, cols);
+  return launch_scan_rule<STATE_RULE_DELTA>(dpt, grid, block, s, q, ldq, k, ldk, v, ldv, decay, beta, g, qscale, state, last_rows, row_seq,
+                                            row_first, row_end, positions, slots, out, cols);
+}
+
+size_t state_floats_per_slot(const StateGeom& g) { return (size_t)2 * g.heads * g.dim * g.vdim; }
+
+int launch_state_out_gate(const float* o, const float* gain, const float* gate, int gate_ld, int gate_silu, void* out, int out_f32,
+                          int heads, int vdim, float eps, int T, cudaStream_t s) {
+  if (T <= 0) return 0;
+  const long units = (long)T * heads;
+  const dim3 grid((unsigned)((units + 3) / 4));
+  if (out_f32) B2_CUDA_OK(b2_launch(state_out_gate_kernel<float>, grid, dim3(128), 0, s, o, gain, gate, gate_ld, gate_silu, (float*)out, heads, vdim, eps, T));
+  else B2_CUDA_OK(b2_launch(state_out_gate_kernel<bf16>, grid, dim3(128), 0, s, o, gain, gate, gate_ld, gate_silu, (bf16*)out, heads, vdim, eps, T));
+  return 0;
+}
+
+}  // namespace b2

@@ -95,8 +95,27 @@ struct ListLayer {
                               // layout and attention runs on attn_prefill_tc.cu / attn_decode.cu
   float *gain1b = nullptr, *gain2b = nullptr, *qkv_bias = nullptr, *o_bias = nullptr, *conv_w = nullptr, *talk = nullptr, *vmix = nullptr;
   float* conv_ring = nullptr; // [sequence slots][taps][q | k | v channels], row = position mod taps: the projected rows a sequence's next convolutions need
+  // Mixers with a matrix state (Bumalix): `wqd` is ONE projection of the layer's norm output -- softmax q | k | v, then the state mixer's
+  // q | k | v | g, then the low-rank first stage a1 ("parallel"); or q | k | v | b | a1 | g1 (delta rule).  The low-rank widths are the
+  // checkpoint tensors' (no config entry names them): a1 / g1 wait on the host until the weights are finalised, when the projection is
+  // re-made with their rows behind the n_fixed rows whose count the config gives.  wo / wo2: output projections of the first / second mixer.
+  int n_fixed = 0, rank_a = 0, rank_g = 0;
+  int off_sq = 0, off_sk = 0, off_sv = 0, off_sg = 0;   // first column of the state mixer's q, k, v, g in the projection's output
+  void *wo2 = nullptr, *sh_up = nullptr, *sh_down = nullptr;   // sh_*: the shared expert (gate | up, down)
+  float *qk_gain = nullptr, *head_gain = nullptr, *a2 = nullptr, *a2_bias = nullptr, *g2 = nullptr, *a_log = nullptr, *out_gain_l = nullptr,
+        *out_gain_r = nullptr, *poly = nullptr;
+  size_t a2_floats = 0, g2_floats = 0;
+  std::vector<uint16_t> a1_host, g1_host;
 };
-inline bool list_arch(int arch) { return arch == B2_ARCH_LERASUN || arch == B2_ARCH_KEDASUN; }
+// One run of a layer.  A looped layer runs once per pass with the same weights (ListLayer) but a cache and state of its own.
+struct ListRun {
+  int layer = 0;
+  bool pass_start = false;     // the loop's input mix x <- W_in [x; x0] comes right before this run
+  int k_region = -1, v_region = -1;
+  float* state = nullptr;      // [sequence slots][2][heads][dim][vdim] fp32 (attn_state.cu)
+  float* ring = nullptr;       // [sequence slots][taps][channels] fp32: the convolutions' last inputs
+};
+inline bool list_arch(int arch) { return arch == B2_ARCH_LERASUN || arch == B2_ARCH_KEDASUN || arch == B2_ARCH_BUMALIX; }
 
 struct Seq {
   bool active = false;
@@ -309,6 +328,13 @@ struct b2_engine {
   int32_t* h_offsets = nullptr;      // pinned: the experts' slot ranges of the step, read back for the per-expert launches
   size_t l_attn_scratch_floats = 0;
   float* dbg_hidden_f32 = nullptr;
+  int dbg_slots = 0;                 // residual-stream captures per forward: embeddings + one per layer run
+  // matrix-state mixers and the layer loop (Bumalix)
+  std::vector<ListRun> runs;         // the order the layers run in
+  int step_portions = 0;             // sequences in the step being run (each brings one portion of tokens)
+  void *l_loop_in = nullptr, *l_cat = nullptr, *l_av2 = nullptr;   // W_in [W][2W]; its input [x | x0]; the second mixer's gated read-out
+  float *l_dec = nullptr, *l_beta = nullptr, *l_gate = nullptr, *l_so = nullptr, *l_mix2 = nullptr, *l_ffd = nullptr, *l_slot_scale = nullptr;
+  size_t l_qd_cols = 0;
 };
 
 namespace {
@@ -1152,6 +1178,261 @@ int forward_heads_list(b2_engine* e, int T, int ntiles, int nlast) {
   return 0;
 }
 
+// Bumalix: n = norm1(h); h <- h + (mixer(n) + ff(n)) on the same fp32 residual stream, one plain-gain RMS norm per layer feeding every
+// branch.  The layers run in the order of e->runs: a looped run of layers appears once per pass, every pass with cache regions and state
+// of its own, and the stream is re-mixed with the embedding output in front of every pass (x <- W_in [x; x0]).  Every projection that
+// reads the norm output is ONE product (softmax q | k | v | state q | k | v | g | low-rank first stage); the softmax half runs on
+// attn_heads.cu over the block table, the state half on attn_state.cu over the sequence slots; the last kernel of a layer adds every
+// branch into the stream and forms the next layer's norm output.
+constexpr float BUMALIX_UNIT_EPS = 1e-6f;   // q and k of the delta rule: x / sqrt(sum(x^2) + 1e-6)
+
+int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
+  const b2_config& c = e->cfg;
+  const int W = c.hidden, f = e->f32 ? 1 : 0;
+  cudaStream_t st = e->stream;
+  auto dbg = [&](int slot) {
+    if ((e->debug_flags & 1) && e->dbg_hidden_f32 != nullptr && T <= e->dbg_cap_tokens && slot < e->dbg_slots)
+      cudaMemcpyAsync(e->dbg_hidden_f32 + (size_t)slot * e->dbg_cap_tokens * W, e->l_h, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st);
+  };
+  auto dense = [&](const void* A, const void* Wt, float* C, int M, int N, int K) -> int { return list_dense(e, A, Wt, C, M, N, K, 1.f); };
+  {
+    KL k(e, B2K_EMBED);
+    if (!k.skip()) B2_TRY(launch_embed_scaled(e->d_tokens, e->l_embed, f, c.embed_scale != 0.f ? c.embed_scale : 1.f, e->l_h, T, W, c.vocab, st));
+  }
+  if (e->l_cat != nullptr) {
+    KL k(e, B2K_MISC);   // x0, the half of W_in's input that every pass shares
+    if (!k.skip()) B2_TRY(launch_store_rows(e->l_h, e->l_cat, f, 2 * W, W, T, W, st));
+  }
+  dbg(0);
+  const PrefillTile* tiles = ntiles > 0 ? e->d_tiles : nullptr;
+  const int portions = ntiles > 0 ? e->step_portions : T;
+  const int32_t* last_rows = ntiles > 0 ? e->d_last_rows : nullptr;
+  const bool use_tc = list_use_tc();
+  bool have_norm = false;   // l_x1 already holds this layer's norm output (the layer before wrote it)
+  for (size_t r = 0; r < e->runs.size(); ++r) {
+    const ListRun& R = e->runs[r];
+    ListLayer& L = e->ll[R.layer];
+    const b2_layer_spec& sp = L.sp;
+    if (R.pass_start) {
+      {
+        KL k(e, B2K_MISC);
+        if (!k.skip()) B2_TRY(launch_store_rows(e->l_h, e->l_cat, f, 2 * W, 0, T, W, st));
+      }
+      KL k(e, B2K_GEMM_O);
+      if (!k.skip()) B2_TRY(dense(e->l_cat, e->l_loop_in, e->l_h, T, W, 2 * W));
+      have_norm = false;
+    }
+    if (!have_norm) {
+      KL k(e, B2K_NORM);
+      if (!k.skip()) B2_TRY(launch_group_norm(e->l_h, L.gain1, e->l_x1, f, T, W, 1, c.rms_eps, nullptr, st));
+    }
+    {
+      KL k(e, B2K_GEMM_QKV);
+      if (!k.skip()) B2_TRY(dense(e->l_x1, L.wqd, e->l_qd, T, L.nqd, W));
+    }
+    const bool two = sp.mixer == B2_MIXER_WINDOW_AND_STATE;
+    if (two) {
+      HeadsGeom g{sp.heads, sp.kv_heads, sp.dim, sp.vdim, 0, 0.f, sp.scale, c.rms_eps, 0, 0, 0, 0.f, sp.window, 0, 0, 0};
+      char* kc = e->regions[R.k_region].base;
+      char* vc = e->regions[R.v_region].base;
+      {
+        KL k(e, B2K_ROPE_KV);
+        if (!k.skip()) B2_TRY(launch_heads_finish_rownorm(e->l_qd, L.nqd, g, L.qkv_bias, L.qk_gain, e->d_slots, e->l_q, kc, vc, f, T, st));
+      }
+      {
+        KL k(e, ntiles > 0 ? B2K_MISC : B2K_ATTN_DECODE);
+        if (!k.skip()) B2_TRY(launch_heads_attention(e->l_q, kc, vc, f, g, e->d_block_table, e->bt_stride, c.block_size, tiles, ntiles, e->d_positions,
+                                                     e->d_seq_lens, e->l_av, f, T, st));
+      }
+      {
+        KL k(e, B2K_GEMM_O);
+        if (!k.skip()) B2_TRY(dense(e->l_av, L.wo, e->l_mix, T, W, sp.heads * sp.vdim));
+      }
+      const StateGeom sg{sp.s_heads, sp.s_heads, sp.s_dim, sp.s_vdim, STATE_RULE_DECAY};
+      {
+        KL k(e, B2K_ACT);   // decay per key channel: sigmoid(A2 (A1 n) + b)^(1 / tau)
+        if (!k.skip()) B2_TRY(launch_lowrank_act(e->l_qd, L.nqd, L.n_fixed, L.rank_a, L.a2, L.a2_bias, LOWRANK_DECAY_SIGMOID_POW, 1.0f / sp.s_tau, nullptr, 0,
+                                                 e->l_dec, T, sp.s_heads * sp.s_dim, st));
+      }
+      {
+        KL k(e, B2K_CHAIN);
+        if (!k.skip()) B2_TRY(launch_state_scan(e->l_qd + L.off_sq, L.nqd, e->l_qd + L.off_sk, L.nqd, e->l_qd + L.off_sv, L.nqd, e->l_dec, nullptr, sg,
+                                                1.0f / sqrtf((float)sp.s_dim), R.state, portions, last_rows, e->d_row_seq, e->d_row_first, e->d_row_end,
+                                                e->d_positions, e->d_slots, e->l_so, st));
+      }
+      {
+        KL k(e, B2K_ACT);
+        if (!k.skip()) B2_TRY(launch_state_out_gate(e->l_so, L.head_gain, e->l_qd + L.off_sg, L.nqd, 1, e->l_av2, f, sp.s_heads, sp.s_vdim, c.rms_eps, T, st));
+      }
+      {
+        KL k(e, B2K_GEMM_O);
+        if (!k.skip()) B2_TRY(dense(e->l_av2, L.wo2, e->l_mix2, T, W, sp.s_heads * sp.s_vdim));
+      }
+    } else {
+      const StateGeom sg{sp.heads, sp.kv_heads, sp.dim, sp.vdim, STATE_RULE_DELTA};
+      const int nqk = sp.kv_heads * sp.dim, C = 2 * nqk + sp.heads * sp.vdim;
+      {
+        KL k(e, B2K_ROPE_KV);
+        if (!k.skip()) B2_TRY(launch_conv_unit_finish(e->l_qd, L.nqd, sg, sp.conv_taps, L.conv_w, R.ring, e->d_row_seq, e->d_row_first, e->d_row_end,
+                                                      e->d_positions, e->d_slots, BUMALIX_UNIT_EPS, e->l_q, e->l_beta, T, st));
+      }
+      {
+        KL k(e, B2K_ACT);   // decay exp(-exp(A_log) softplus(A2 (A1 n) + dt_bias)) and the output gate sigmoid(G2 (G1 n))
+        if (!k.skip()) {
+          B2_TRY(launch_lowrank_act(e->l_qd, L.nqd, L.n_fixed, L.rank_a, L.a2, L.a2_bias, LOWRANK_DECAY_SOFTPLUS, 0.f, L.a_log, sp.dim, e->l_dec, T,
+                                    sp.heads * sp.dim, st));
+          B2_TRY(launch_lowrank_act(e->l_qd, L.nqd, L.n_fixed + L.rank_a, L.rank_g, L.g2, nullptr, LOWRANK_SIGMOID, 0.f, nullptr, 0, e->l_gate, T,
+                                    sp.heads * sp.vdim, st));
+        }
+      }
+      {
+        KL k(e, B2K_CHAIN);
+        if (!k.skip()) B2_TRY(launch_state_scan(e->l_q, C, e->l_q + nqk, C, e->l_q + 2 * nqk, C, e->l_dec, e->l_beta, sg, 1.0f, R.state, portions, last_rows,
+                                                e->d_row_seq, e->d_row_first, e->d_row_end, e->d_positions, e->d_slots, e->l_so, st));
+      }
+      {
+        KL k(e, B2K_ACT);
+        if (!k.skip()) B2_TRY(launch_state_out_gate(e->l_so, L.head_gain, e->l_gate, sp.heads * sp.vdim, 0, e->l_av, f, sp.heads, sp.vdim, c.rms_eps, T, st));
+      }
+      {
+        KL k(e, B2K_GEMM_O);
+        if (!k.skip()) B2_TRY(dense(e->l_av, L.wo, e->l_mix, T, W, sp.heads * sp.vdim));
+      }
+    }
+    const float* d1 = nullptr;
+    const float* yr = nullptr;
+    if (sp.ff == B2_FF_POLYNORM) {
+      {
+        KL k(e, B2K_GEMM_GATEUP);
+        if (!k.skip()) B2_TRY(dense(e->l_x1, L.up, e->l_upf, T, sp.ff_dim, W));
+      }
+      {
+        KL k(e, B2K_ACT);
+        if (!k.skip()) B2_TRY(launch_poly_norm(e->l_upf, L.poly, e->l_act, f, T, sp.ff_dim, c.rms_eps, st));
+      }
+      {
+        KL k(e, B2K_GEMM_DOWN);
+        if (!k.skip()) B2_TRY(dense(e->l_act, L.down, e->l_ffd, T, W, sp.ff_dim));
+      }
+      d1 = e->l_ffd;
+    } else if (sp.ff == B2_FF_SCALED_GATED_EXPERTS) {
+      const RouteGeom rg{sp.experts, sp.top, 1, 1, 1};
+      const int F = sp.ff_dim, pairs = T * sp.top;
+      {
+        KL k(e, B2K_ACT);
+        if (!k.skip()) B2_TRY(launch_route(e->l_x1, f, L.router, nullptr, rg, e->l_idx, e->l_rw, T, W, st));
+      }
+      {
+        KL k(e, B2K_MISC);
+        if (!k.skip()) {
+          B2_TRY(launch_route_permute(e->l_idx, T, sp.top, sp.experts, e->l_offsets, e->l_offsets_stride, e->l_slot_token, e->l_pair_slot, st));
+          B2_TRY(launch_route_slot_weights(e->l_rw, e->l_pair_slot, e->l_slot_scale, pairs, st));
+        }
+      }
+      // The weight multiplies the expert's input: gate and up are linear in it, so it is applied to their fp32 sums inside the
+      // activation.  Prompt-sized bf16 steps run expert by expert on the tcgen05 projection kernel (rows gathered into expert
+      // order, slot ranges read back); everything else as ragged groups.
+      const bool tc_experts = use_tc && !f && ntiles > 0 && e->l_xperm != nullptr && pairs >= LIST_TC_EXPERT_ROWS && W % 64 == 0 && F % 64 == 0 &&
+                              W >= 128 && F >= 64 && e->skip_mask == 0;
+      if (tc_experts) {
+        B2_CUDA_OK(cudaMemcpyAsync(e->h_offsets, e->l_offsets, (size_t)(sp.experts + 1) * 4, cudaMemcpyDeviceToHost, st));
+        {
+          KL k(e, B2K_MISC);
+          B2_TRY(launch_gather_rows((const bf16*)e->l_x1, e->l_slot_token, e->l_xperm, pairs, W, st));
+        }
+        B2_CUDA_OK(cudaStreamSynchronize(st));
+        const int32_t* off = e->h_offsets;
+        B2_REQUIRE(off[0] == 0 && off[sp.experts] == pairs, "layer %d: the experts' slot ranges do not cover the step's %d pairs", R.layer, pairs);
+        {
+          KL k(e, B2K_GEMM_GATEUP);
+          for (int x = 0; x < sp.experts; ++x)
+            if (off[x + 1] > off[x])
+              B2_TRY(dense(e->l_xperm + (size_t)off[x] * W, (const bf16*)L.up + (size_t)x * 2 * F * W, e->l_upf + (size_t)off[x] * 2 * F, off[x + 1] - off[x],
+                           2 * F, W));
+        }
+        {
+          KL k(e, B2K_ACT);
+          B2_TRY(launch_silu_gate(e->l_upf, e->l_slot_scale, nullptr, e->l_act, 0, pairs, F, st));
+        }
+        {
+          KL k(e, B2K_GEMM_DOWN);
+          for (int x = 0; x < sp.experts; ++x)
+            if (off[x + 1] > off[x])
+              B2_TRY(dense((const bf16*)e->l_act + (size_t)off[x] * F, (const bf16*)L.down + (size_t)x * W * F, e->l_y + (size_t)off[x] * W,
+                           off[x + 1] - off[x], W, F));
+        }
+      } else {
+        const int max_tiles = std::min(e->l_tiles_cap, (pairs + any_gemm_tile_rows() - 1) / any_gemm_tile_rows() + sp.experts);
+        if (pairs > any_gemm_ragged_rows_limit() || W > 16384 || 2 * F > 16384) {
+          KL k(e, B2K_MISC);
+          if (!k.skip()) B2_TRY(launch_ragged_tiles(e->l_offsets, sp.experts, e->l_tile_group, e->l_tile_row0, e->l_ntiles, max_tiles, st));
+        }
+        AnyGemm a;
+        a.tile_group = e->l_tile_group; a.tile_row0 = e->l_tile_row0; a.n_tiles = e->l_ntiles; a.group_offsets = e->l_offsets;
+        {
+          KL k(e, B2K_GEMM_GATEUP);  // gate | up of every (token, choice) pair in expert order, fp32 sums
+          a.A = e->l_x1; a.a_rows = e->l_slot_token; a.W = L.up; a.C = e->l_upf; a.N = 2 * F; a.K = W; a.lda = W; a.ldw = W; a.ldc = 2 * F;
+          a.w_bs = (long)2 * F * W; a.epilogue = ANY_EPI_STORE;
+          if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, max_tiles, st, pairs, sp.experts));
+        }
+        {
+          KL k(e, B2K_ACT);
+          if (!k.skip()) B2_TRY(launch_silu_gate(e->l_upf, e->l_slot_scale, nullptr, e->l_act, f, pairs, F, st));
+        }
+        {
+          KL k(e, B2K_GEMM_DOWN);
+          a.A = e->l_act; a.a_rows = nullptr; a.W = L.down; a.C = e->l_y; a.N = W; a.K = F; a.lda = F; a.ldw = F; a.ldc = W;
+          a.w_bs = (long)W * F; a.epilogue = ANY_EPI_STORE;
+          if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, max_tiles, st, pairs, sp.experts));
+        }
+      }
+      yr = e->l_y;
+      if (sp.shared_ff > 0) {
+        {
+          KL k(e, B2K_GEMM_GATEUP);
+          if (!k.skip()) B2_TRY(dense(e->l_x1, L.sh_up, e->l_upf, T, 2 * sp.shared_ff, W));
+        }
+        {
+          KL k(e, B2K_ACT);
+          if (!k.skip()) B2_TRY(launch_silu_gate(e->l_upf, nullptr, nullptr, e->l_act, f, T, sp.shared_ff, st));
+        }
+        {
+          KL k(e, B2K_GEMM_DOWN);
+          if (!k.skip()) B2_TRY(dense(e->l_act, L.sh_down, e->l_ffd, T, W, sp.shared_ff));
+        }
+        d1 = e->l_ffd;
+      }
+    }
+    {
+      KL k(e, B2K_NORM);  // h += (mixer + ff); the next layer's norm output, unless the loop's input mix comes first
+      const bool next_plain = r + 1 < e->runs.size() && !e->runs[r + 1].pass_start && e->skip_mask == 0;
+      const float* gn = next_plain ? e->ll[e->runs[r + 1].layer].gain1 : nullptr;
+      if (!k.skip())
+        B2_TRY(launch_branch_add(e->l_h, e->l_mix, two ? L.out_gain_l : nullptr, two ? e->l_mix2 : nullptr, two ? L.out_gain_r : nullptr, two ? 0.5f : 1.0f, d1,
+                                 yr, e->l_pair_slot, sp.top, T, W, c.rms_eps, st, gn, gn ? e->l_x1 : nullptr, f));
+      have_norm = gn != nullptr;
+    }
+    dbg((int)r + 1);
+  }
+  {
+    KL k(e, B2K_NORM);
+    if (!k.skip()) B2_TRY(launch_group_norm(e->l_h, e->l_final_gain, e->l_xl, f, nlast, W, 1, c.rms_eps, ntiles > 0 ? e->d_last_rows : nullptr, st));
+  }
+  {
+    KL k(e, B2K_LMHEAD);
+    if (!k.skip()) B2_TRY(dense(e->l_xl, e->l_head, e->l_logits, nlast, c.vocab, W));
+  }
+  {
+    KL k(e, B2K_MISC);
+    bf16* lb = (e->debug_flags & 2) ? e->logits : nullptr;
+    if (!k.skip()) {
+      if (c.logit_softcap > 0.f) B2_TRY(launch_softcap(e->l_logits, (size_t)nlast * c.vocab, c.logit_softcap, st));
+      B2_TRY(launch_logits_finish(e->l_logits, e->d_out_tokens, lb, bucket_batch(std::max(c.max_seqs, 1)), nlast, c.vocab, e->v_pad, st));
+    }
+  }
+  return 0;
+}
+
 // Two-lane decode.  At batch 64 a decode step is two things that do not overlap when they depend on each other: the
 // attention pass of a layer (HBM-bound, about half the step) and the eight small kernels between two attention
 // passes (a chain of dependent launches that moves 31 MB of weights in ~30 us: latency-bound, HBM nearly idle).
@@ -1172,6 +1453,7 @@ int forward(b2_engine* e, int T, int ntiles, int nlast, int attn_split) {
   (void)attn_split;
   if (c.arch == B2_ARCH_LERASUN) return forward_list(e, T, ntiles, nlast);
   if (c.arch == B2_ARCH_KEDASUN) return forward_heads_list(e, T, ntiles, nlast);
+  if (c.arch == B2_ARCH_BUMALIX) return forward_state_list(e, T, ntiles, nlast);
   if (c.arch == B2_ARCH_OPT) return forward_opt(e, T, ntiles, nlast);
   if (ntiles == 0 && e->use_chain == 2 && e->fused_ok && c.arch == B2_ARCH_QWEN3 && !(e->debug_flags & 1) &&
       e->force_gemm_impl != 0 && T > e->simt_max_tokens && T <= 64 && e->skip_mask == 0)
@@ -1556,7 +1838,8 @@ int list_tensor(b2_engine* e, const std::string& name, const void* host, size_t 
   if (name == "embed") { B2_TRY(want((size_t)c.vocab * W)); return done(put_operand(e, e->l_embed, 0, src, (size_t)c.vocab * W)); }
   if (name == "head") { B2_TRY(want((size_t)c.vocab * W)); return done(put_operand(e, e->l_head, 0, src, (size_t)c.vocab * W)); }
   if (name == "embed.norm") { B2_TRY(want(W)); return done(put_f32(e->l_embed_gain, src, W, 1.0f)); }
-  if (name == "final.norm") { B2_TRY(want(W)); return done(put_f32(e->l_final_gain, src, W, c.arch == B2_ARCH_KEDASUN ? 0.0f : 1.0f)); }
+  if (name == "final.norm") { B2_TRY(want(W)); return done(put_f32(e->l_final_gain, src, W, c.arch == B2_ARCH_LERASUN ? 1.0f : 0.0f)); }
+  if (c.arch == B2_ARCH_BUMALIX && name == "loop.in" && e->l_loop_in) { B2_TRY(want(W * 2 * W)); return done(put_operand(e, e->l_loop_in, 0, src, W * 2 * W)); }
   size_t dot = name.find('.');
   if (name.size() < 3 || name[0] != 'l' || dot == std::string::npos || dot < 2) {
     b2_set_error("unknown tensor name %s", name.c_str());
@@ -1571,6 +1854,92 @@ int list_tensor(b2_engine* e, const std::string& name, const void* host, size_t 
   const b2_layer_spec& sp = L.sp;
   const std::string rest = name.substr(dot + 1);
   const size_t H = sp.heads, dn = sp.dim, dr = sp.rot_dim, dv = sp.vdim, r = sp.kv_rank, ff = sp.ff_dim;
+  if (c.arch == B2_ARCH_BUMALIX) {
+    const bool two = sp.mixer == B2_MIXER_WINDOW_AND_STATE;
+    // a tensor whose size the config does not give: the number of values decides (a fresh fp32 copy on the device)
+    auto any_f32 = [&](float** dst, size_t* floats) -> int {
+      B2_REQUIRE(nbytes >= 2 && nbytes % 2 == 0, "tensor %s: %zu bytes", name.c_str(), nbytes);
+      if (*dst) cudaFree(*dst);
+      *dst = nullptr;
+      B2_TRY(dalloc(dst, nbytes / 2));
+      *floats = nbytes / 2;
+      e->weight_bytes += (int64_t)(nbytes * 2);
+      return put_f32(*dst, src, nbytes / 2, 0.0f);
+    };
+    auto low_rank = [&](std::vector<uint16_t>* host, int* rank) -> int {   // [rank][W], rank from the size
+      B2_REQUIRE(nbytes >= 2 * W && nbytes % (2 * W) == 0, "tensor %s: %zu bytes are not rows of %zu values", name.c_str(), nbytes, W);
+      B2_REQUIRE(L.nqd == L.n_fixed, "tensor %s: the layer's projection is already joined", name.c_str());
+      host->assign(src, src + nbytes / 2);
+      *rank = (int)(nbytes / (2 * W));
+      return 0;
+    };
+    if (rest == "norm1") { B2_TRY(want(W)); return done(put_f32(L.gain1, src, W, 0.0f)); }
+    if (two) {
+      const size_t nq = L.nq, nk = L.nk, nv = L.nv, sh = sp.s_heads, sd = sp.s_dim, sv = sp.s_vdim;
+      if (rest == "mix.left.q") { B2_TRY(want(nq * W)); return done(put_operand(e, L.wqd, 0, src, nq * W)); }
+      if (rest == "mix.left.k") { B2_TRY(want(nk * W)); return done(put_operand(e, L.wqd, nq * W, src, nk * W)); }
+      if (rest == "mix.left.v") { B2_TRY(want(nv * W)); return done(put_operand(e, L.wqd, (nq + nk) * W, src, nv * W)); }
+      if (rest == "mix.left.q.b") { B2_TRY(want(nq)); return done(put_f32(L.qkv_bias, src, nq, 0.0f)); }
+      if (rest == "mix.left.k.b") { B2_TRY(want(nk)); return done(put_f32(L.qkv_bias + nq, src, nk, 0.0f)); }
+      if (rest == "mix.left.v.b") { B2_TRY(want(nv)); return done(put_f32(L.qkv_bias + nq + nk, src, nv, 0.0f)); }
+      if (rest == "mix.left.q.norm") { B2_TRY(want(nq)); return done(put_f32(L.qk_gain, src, nq, 0.0f)); }
+      if (rest == "mix.left.k.norm") { B2_TRY(want(nk)); return done(put_f32(L.qk_gain + nq, src, nk, 0.0f)); }
+      if (rest == "mix.left.o") { B2_TRY(want(W * H * dv)); return done(put_operand(e, L.wo, 0, src, W * H * dv)); }
+      if (rest == "mix.left.out") { B2_TRY(want(W)); return done(put_f32(L.out_gain_l, src, W, 0.0f)); }
+      if (rest == "mix.right.q") { B2_TRY(want(sh * sd * W)); return done(put_operand(e, L.wqd, (size_t)L.off_sq * W, src, sh * sd * W)); }
+      if (rest == "mix.right.k") { B2_TRY(want(sh * sd * W)); return done(put_operand(e, L.wqd, (size_t)L.off_sk * W, src, sh * sd * W)); }
+      if (rest == "mix.right.v") { B2_TRY(want(sh * sv * W)); return done(put_operand(e, L.wqd, (size_t)L.off_sv * W, src, sh * sv * W)); }
+      if (rest == "mix.right.g") { B2_TRY(want(sh * sv * W)); return done(put_operand(e, L.wqd, (size_t)L.off_sg * W, src, sh * sv * W)); }
+      if (rest == "mix.right.o") { B2_TRY(want(W * sh * sv)); return done(put_operand(e, L.wo2, 0, src, W * sh * sv)); }
+      if (rest == "mix.right.norm") { B2_TRY(want(sv)); return done(put_f32(L.head_gain, src, sv, 0.0f)); }
+      if (rest == "mix.right.a1") return done(low_rank(&L.a1_host, &L.rank_a));
+      if (rest == "mix.right.a2") return done(any_f32(&L.a2, &L.a2_floats));
+      if (rest == "mix.right.a2.b") { B2_TRY(want(sh * sd)); return done(put_f32(L.a2_bias, src, sh * sd, 0.0f)); }
+      if (rest == "mix.right.out") { B2_TRY(want(W)); return done(put_f32(L.out_gain_r, src, W, 0.0f)); }
+    } else {
+      const size_t nqk = (size_t)sp.kv_heads * dn, nvv = H * dv, taps = sp.conv_taps;
+      if (rest == "mix.q") { B2_TRY(want(nqk * W)); return done(put_operand(e, L.wqd, 0, src, nqk * W)); }
+      if (rest == "mix.k") { B2_TRY(want(nqk * W)); return done(put_operand(e, L.wqd, nqk * W, src, nqk * W)); }
+      if (rest == "mix.v") { B2_TRY(want(nvv * W)); return done(put_operand(e, L.wqd, 2 * nqk * W, src, nvv * W)); }
+      if (rest == "mix.b") { B2_TRY(want(H * W)); return done(put_operand(e, L.wqd, (2 * nqk + nvv) * W, src, H * W)); }
+      if (rest == "mix.q.conv") { B2_TRY(want(nqk * taps)); return done(put_f32(L.conv_w, src, nqk * taps, 0.0f)); }
+      if (rest == "mix.k.conv") { B2_TRY(want(nqk * taps)); return done(put_f32(L.conv_w + nqk * taps, src, nqk * taps, 0.0f)); }
+      if (rest == "mix.v.conv") { B2_TRY(want(nvv * taps)); return done(put_f32(L.conv_w + 2 * nqk * taps, src, nvv * taps, 0.0f)); }
+      if (rest == "mix.A_log") { B2_TRY(want(H)); return done(put_f32(L.a_log, src, H, 0.0f)); }
+      if (rest == "mix.norm") { B2_TRY(want(dv)); return done(put_f32(L.head_gain, src, dv, 0.0f)); }
+      if (rest == "mix.a1") return done(low_rank(&L.a1_host, &L.rank_a));
+      if (rest == "mix.a2") return done(any_f32(&L.a2, &L.a2_floats));
+      if (rest == "mix.dt_bias") { B2_TRY(want(H * dn)); return done(put_f32(L.a2_bias, src, H * dn, 0.0f)); }
+      if (rest == "mix.g1") return done(low_rank(&L.g1_host, &L.rank_g));
+      if (rest == "mix.g2") return done(any_f32(&L.g2, &L.g2_floats));
+      if (rest == "mix.o") { B2_TRY(want(W * nvv)); return done(put_operand(e, L.wo, 0, src, W * nvv)); }
+    }
+    if (sp.ff == B2_FF_POLYNORM) {
+      if (rest == "mlp.up") { B2_TRY(want(ff * W)); return done(put_operand(e, L.up, 0, src, ff * W)); }
+      if (rest == "mlp.down") { B2_TRY(want(W * ff)); return done(put_operand(e, L.down, 0, src, W * ff)); }
+      if (rest == "mlp.act") { B2_TRY(want(4)); return done(put_f32(L.poly, src, 4, 0.0f)); }
+    } else if (sp.ff == B2_FF_SCALED_GATED_EXPERTS) {
+      const size_t sf = sp.shared_ff;
+      if (rest == "mlp.router") { B2_TRY(want((size_t)sp.experts * W)); return done(put_f32(L.router, src, (size_t)sp.experts * W, 0.0f)); }
+      if (sf > 0 && rest == "mlp.shared.gate") { B2_TRY(want(sf * W)); return done(put_operand(e, L.sh_up, 0, src, sf * W)); }
+      if (sf > 0 && rest == "mlp.shared.up") { B2_TRY(want(sf * W)); return done(put_operand(e, L.sh_up, sf * W, src, sf * W)); }
+      if (sf > 0 && rest == "mlp.shared.down") { B2_TRY(want(W * sf)); return done(put_operand(e, L.sh_down, 0, src, W * sf)); }
+      if (rest.compare(0, 5, "mlp.e") == 0) {
+        size_t d2 = rest.find('.', 5);
+        if (d2 != std::string::npos) {
+          const int ex = atoi(rest.substr(5, d2 - 5).c_str());
+          const std::string which = rest.substr(d2 + 1);
+          if (ex >= 0 && ex < sp.experts) {   // gate rows, then up rows, expert by expert: one product gives both
+            if (which == "gate") { B2_TRY(want(ff * W)); return done(put_operand(e, L.up, (size_t)ex * 2 * ff * W, src, ff * W)); }
+            if (which == "up") { B2_TRY(want(ff * W)); return done(put_operand(e, L.up, ((size_t)ex * 2 + 1) * ff * W, src, ff * W)); }
+            if (which == "down") { B2_TRY(want(W * ff)); return done(put_operand(e, L.down, (size_t)ex * W * ff, src, W * ff)); }
+          }
+        }
+      }
+    }
+    b2_set_error("unknown tensor name %s", name.c_str());
+    return -22;
+  }
   if (c.arch == B2_ARCH_KEDASUN) {
     const size_t nq = L.nq, nk = L.nk, nv = L.nv, taps = sp.conv_taps;
     const bool conv = sp.mixer == B2_MIXER_CONV_ATTENTION;
@@ -1771,8 +2140,268 @@ int heads_engine_alloc(b2_engine* e) {
   return 0;
 }
 
+// The same for the family with matrix-state mixers and a layer loop (Bumalix).  The fused projection of a layer and the buffer its
+// output goes to are sized when the weights are finalised (state_finalize): the low-rank widths come with the tensors.
+int state_engine_alloc(b2_engine* e) {
+  const b2_config& c = e->cfg;
+  const size_t W = c.hidden, es = e->esz;
+  B2_REQUIRE(!e->specs.empty() && (int)e->specs.size() == c.num_layers, "Bumalix: layer_specs missing");
+  B2_REQUIRE(c.hidden >= 1 && c.vocab >= 1 && c.num_layers >= 1, "Bumalix: bad sizes");
+  B2_REQUIRE(c.loop_times >= 0 && (c.loop_times == 0 || (c.loop_start >= 0 && c.loop_start <= c.loop_stop && c.loop_stop <= c.num_layers)),
+             "Bumalix: loop [%d, %d) x %d outside the %d layers", c.loop_start, c.loop_stop, c.loop_times, c.num_layers);
+  auto xalloc = [&](void** p, size_t elems) -> int {
+    char* q = nullptr;
+    B2_TRY(dalloc(&q, std::max<size_t>(elems, 1) * es));
+    *p = q;
+    e->weight_bytes += (int64_t)(elems * es);
+    return 0;
+  };
+  auto falloc = [&](float** p, size_t n) -> int {
+    B2_TRY(dalloc(p, std::max<size_t>(n, 1)));
+    B2_CUDA_OK(cudaMemset(*p, 0, std::max<size_t>(n, 1) * 4));
+    e->weight_bytes += (int64_t)(n * 4);
+    return 0;
+  };
+  e->weight_bytes = 0;
+  B2_TRY(xalloc(&e->l_embed, (size_t)c.vocab * W));
+  B2_TRY(xalloc(&e->l_head, (size_t)c.vocab * W));
+  B2_TRY(falloc(&e->l_final_gain, W));
+  const bool looped = c.loop_times > 0 && c.loop_stop > c.loop_start;
+  if (looped) B2_TRY(xalloc(&e->l_loop_in, W * 2 * W));
+  e->ll.resize(c.num_layers);
+  size_t max_q = 1, max_dec = 1, max_hv = 1, max_hv2 = 1, max_heads = 1, max_up = 1, max_act = 1;
+  int max_top = 1, max_exp = 1;
+  for (int l = 0; l < c.num_layers; ++l) {
+    ListLayer& L = e->ll[l];
+    L.sp = e->specs[l];
+    const b2_layer_spec& sp = L.sp;
+    const bool two = sp.mixer == B2_MIXER_WINDOW_AND_STATE;
+    B2_REQUIRE(two || sp.mixer == B2_MIXER_DELTA_STATE, "layer %d: mixer kind %d not built for this family", l, sp.mixer);
+    B2_REQUIRE(sp.heads >= 1 && sp.kv_heads >= 1 && sp.heads % sp.kv_heads == 0 && sp.dim >= 1 && sp.vdim >= 1,
+               "layer %d: bad mixer sizes (heads %d, kv_heads %d, dim %d, vdim %d)", l, sp.heads, sp.kv_heads, sp.dim, sp.vdim);
+    B2_TRY(falloc(&L.gain1, W));
+    if (two) {
+      B2_REQUIRE(sp.s_heads >= 1 && sp.s_dim >= 1 && sp.s_dim <= 256 && sp.s_vdim >= 1 && sp.s_tau > 0.f && sp.window >= 0,
+                 "layer %d: bad state-mixer sizes (heads %d, dim %d (at most 256), vdim %d, tau %g)", l, sp.s_heads, sp.s_dim, sp.s_vdim, (double)sp.s_tau);
+      L.nq = sp.heads * sp.dim;
+      L.nk = sp.kv_heads * sp.dim;
+      L.nv = sp.kv_heads * sp.vdim;
+      L.off_sq = L.nq + L.nk + L.nv;
+      L.off_sk = L.off_sq + sp.s_heads * sp.s_dim;
+      L.off_sv = L.off_sk + sp.s_heads * sp.s_dim;
+      L.off_sg = L.off_sv + sp.s_heads * sp.s_vdim;
+      L.n_fixed = L.off_sg + sp.s_heads * sp.s_vdim;
+      B2_TRY(falloc(&L.qkv_bias, (size_t)L.off_sq));
+      B2_TRY(falloc(&L.qk_gain, (size_t)L.nq + L.nk));
+      B2_TRY(xalloc(&L.wo, W * sp.heads * sp.vdim));
+      B2_TRY(xalloc(&L.wo2, W * sp.s_heads * sp.s_vdim));
+      B2_TRY(falloc(&L.head_gain, sp.s_vdim));
+      B2_TRY(falloc(&L.a2_bias, (size_t)sp.s_heads * sp.s_dim));
+      B2_TRY(falloc(&L.out_gain_l, W));
+      B2_TRY(falloc(&L.out_gain_r, W));
+      max_q = std::max(max_q, (size_t)L.nq);
+      max_dec = std::max(max_dec, (size_t)sp.s_heads * sp.s_dim);
+      max_hv = std::max({max_hv, (size_t)sp.heads * sp.vdim, (size_t)sp.s_heads * sp.s_vdim});
+      max_hv2 = std::max(max_hv2, (size_t)sp.s_heads * sp.s_vdim);
+      max_heads = std::max(max_heads, (size_t)sp.s_heads);
+    } else {
+      B2_REQUIRE(sp.conv_taps >= 1 && sp.dim <= 256, "layer %d: the delta rule needs at least one convolution tap and a key width of at most 256", l);
+      const size_t nqk = (size_t)sp.kv_heads * sp.dim, C = 2 * nqk + (size_t)sp.heads * sp.vdim;
+      L.n_fixed = (int)(C + sp.heads);
+      B2_TRY(falloc(&L.conv_w, C * sp.conv_taps));
+      B2_TRY(falloc(&L.a_log, sp.heads));
+      B2_TRY(falloc(&L.head_gain, sp.vdim));
+      B2_TRY(falloc(&L.a2_bias, (size_t)sp.heads * sp.dim));
+      B2_TRY(xalloc(&L.wo, W * sp.heads * sp.vdim));
+      max_q = std::max(max_q, C);
+      max_dec = std::max(max_dec, (size_t)sp.heads * sp.dim);
+      max_hv = std::max(max_hv, (size_t)sp.heads * sp.vdim);
+      max_heads = std::max(max_heads, (size_t)sp.heads);
+    }
+    L.nqd = L.n_fixed;
+    B2_TRY(xalloc(&L.wqd, (size_t)L.n_fixed * W));
+    if (sp.ff == B2_FF_POLYNORM) {
+      B2_REQUIRE(sp.ff_dim >= 1, "layer %d: bad feed-forward width", l);
+      B2_TRY(xalloc(&L.up, (size_t)sp.ff_dim * W));
+      B2_TRY(xalloc(&L.down, W * sp.ff_dim));
+      B2_TRY(falloc(&L.poly, 4));
+      max_up = std::max(max_up, (size_t)sp.ff_dim);
+      max_act = std::max(max_act, (size_t)sp.ff_dim);
+    } else if (sp.ff == B2_FF_SCALED_GATED_EXPERTS) {
+      B2_REQUIRE(sp.experts >= 1 && sp.top >= 1 && sp.top <= sp.experts && sp.ff_dim >= 1 && sp.shared_ff >= 0,
+                 "layer %d: bad router sizes (experts %d, top %d, ff %d)", l, sp.experts, sp.top, sp.ff_dim);
+      B2_TRY(falloc(&L.router, (size_t)sp.experts * W));
+      B2_TRY(xalloc(&L.up, (size_t)sp.experts * 2 * sp.ff_dim * W));
+      B2_TRY(xalloc(&L.down, (size_t)sp.experts * W * sp.ff_dim));
+      if (sp.shared_ff > 0) {
+        B2_TRY(xalloc(&L.sh_up, (size_t)2 * sp.shared_ff * W));
+        B2_TRY(xalloc(&L.sh_down, W * sp.shared_ff));
+      }
+      max_top = std::max(max_top, sp.top);
+      max_exp = std::max(max_exp, sp.experts);
+      max_up = std::max({max_up, (size_t)sp.top * 2 * sp.ff_dim, (size_t)2 * sp.shared_ff});
+      max_act = std::max({max_act, (size_t)sp.top * sp.ff_dim, (size_t)sp.shared_ff});
+    } else {
+      B2_REQUIRE(sp.ff == B2_FF_NONE, "layer %d: feed-forward kind %d not built for this family", l, sp.ff);
+    }
+  }
+  // ---- the order the layers run in, and the state of every run ----
+  auto add_run = [&](int layer, bool pass_start) -> int {
+    ListRun R;
+    R.layer = layer;
+    R.pass_start = pass_start;
+    const b2_layer_spec& sp = e->ll[layer].sp;
+    const bool two = sp.mixer == B2_MIXER_WINDOW_AND_STATE;
+    const StateGeom sg{two ? sp.s_heads : sp.heads, two ? sp.s_heads : sp.kv_heads, two ? sp.s_dim : sp.dim, two ? sp.s_vdim : sp.vdim, 0};
+    const size_t sf = (size_t)c.max_seqs * state_floats_per_slot(sg);
+    B2_TRY(dalloc(&R.state, sf));
+    B2_CUDA_OK(cudaMemset(R.state, 0, sf * 4));
+    if (!two && sp.conv_taps > 1) {
+      const size_t rf = (size_t)c.max_seqs * sp.conv_taps * (2 * (size_t)sp.kv_heads * sp.dim + (size_t)sp.heads * sp.vdim);
+      B2_TRY(dalloc(&R.ring, rf));
+      B2_CUDA_OK(cudaMemset(R.ring, 0, rf * 4));
+    }
+    e->runs.push_back(R);
+    return 0;
+  };
+  if (!looped) {
+    for (int l = 0; l < c.num_layers; ++l) B2_TRY(add_run(l, false));
+  } else {
+    for (int l = 0; l < c.loop_start; ++l) B2_TRY(add_run(l, false));
+    for (int t = 0; t < c.loop_times; ++t)
+      for (int l = c.loop_start; l < c.loop_stop; ++l) B2_TRY(add_run(l, l == c.loop_start));
+    for (int l = c.loop_stop; l < c.num_layers; ++l) B2_TRY(add_run(l, false));
+  }
+  e->l_has_state = true;
+  e->dbg_slots = (int)e->runs.size() + 1;
+  // ---- activations ----
+  e->cap_tokens = ((std::max(c.max_batch_tokens, c.max_seqs) + 255) / 256) * 256;
+  const size_t Tc = e->cap_tokens;
+  e->l_rows_cap = (int)(Tc + bucket_batch(c.max_seqs));
+  e->l_max_top = max_top;
+  e->v_pad = (c.vocab + 7) / 8 * 8;
+  auto aalloc = [&](void** p, size_t elems) -> int {
+    char* q = nullptr;
+    B2_TRY(dalloc(&q, elems * es));
+    *p = q;
+    return 0;
+  };
+  B2_TRY(dalloc(&e->l_h, Tc * W));
+  B2_TRY(dalloc(&e->l_q, Tc * max_q));
+  B2_TRY(dalloc(&e->l_dec, Tc * max_dec));
+  B2_TRY(dalloc(&e->l_beta, Tc * max_heads));
+  B2_TRY(dalloc(&e->l_gate, Tc * max_hv));
+  B2_TRY(dalloc(&e->l_so, Tc * max_hv));
+  B2_TRY(dalloc(&e->l_mix, Tc * W));
+  B2_TRY(dalloc(&e->l_mix2, Tc * W));
+  B2_TRY(dalloc(&e->l_ffd, Tc * W));
+  B2_TRY(dalloc(&e->l_y, Tc * max_top * W));
+  B2_TRY(dalloc(&e->l_upf, Tc * max_up));
+  B2_TRY(dalloc(&e->l_rw, Tc * max_top));
+  B2_TRY(dalloc(&e->l_slot_scale, Tc * max_top));
+  B2_TRY(dalloc(&e->l_logits, (size_t)e->l_rows_cap * c.vocab));
+  B2_TRY(aalloc(&e->l_x1, Tc * W));
+  if (looped) B2_TRY(aalloc(&e->l_cat, Tc * 2 * W));
+  B2_TRY(aalloc(&e->l_av, Tc * max_hv));
+  B2_TRY(aalloc(&e->l_av2, Tc * max_hv2));
+  B2_TRY(aalloc(&e->l_act, Tc * max_act));
+  B2_TRY(aalloc(&e->l_xl, (size_t)e->l_rows_cap * W));
+  B2_TRY(dalloc(&e->l_idx, Tc * max_top));
+  e->l_offsets_stride = max_exp + 1;
+  B2_TRY(dalloc(&e->l_offsets, (size_t)3 * (max_exp + 1)));
+  B2_CUDA_OK(cudaMemset(e->l_offsets, 0, (size_t)3 * (max_exp + 1) * 4));
+  B2_TRY(dalloc(&e->l_slot_token, Tc * max_top));
+  B2_TRY(dalloc(&e->l_pair_slot, Tc * max_top));
+  e->l_tiles_cap = (int)(Tc * max_top / any_gemm_tile_rows() + max_exp + 1);
+  B2_TRY(dalloc(&e->l_tile_group, (size_t)e->l_tiles_cap));
+  B2_TRY(dalloc(&e->l_tile_row0, (size_t)e->l_tiles_cap));
+  B2_TRY(dalloc(&e->l_ntiles, (size_t)1));
+  if (!e->f32 && Tc * max_top >= (size_t)LIST_TC_EXPERT_ROWS && max_exp > 1) {   // prompt-sized expert products on the tcgen05 projection kernel
+    B2_TRY(dalloc(&e->l_xperm, Tc * max_top * W));
+    B2_CUDA_OK(cudaMallocHost(&e->h_offsets, (size_t)(max_exp + 1) * sizeof(int32_t)));
+  }
+  B2_CUDA_OK(cudaMemset(e->l_ntiles, 0, 4));
+  B2_CUDA_OK(cudaMemset(e->l_pair_slot, 0, Tc * max_top * 4));
+  B2_CUDA_OK(cudaMemset(e->l_slot_scale, 0, Tc * max_top * 4));
+  B2_TRY(dalloc(&e->d_row_seq, Tc));
+  B2_TRY(dalloc(&e->d_row_first, Tc));
+  B2_TRY(dalloc(&e->d_row_end, Tc));
+  B2_CUDA_OK(cudaMemset(e->d_row_seq, 0, Tc * 4));
+  B2_CUDA_OK(cudaMemset(e->d_row_first, 0, Tc * 4));
+  B2_CUDA_OK(cudaMemset(e->d_row_end, 0, Tc * 4));
+  return 0;
+}
+
+// Names of the tensors a Bumalix checkpoint must hold.
+std::vector<std::string> state_tensor_names(const b2_engine* e) {
+  std::vector<std::string> n = {"embed", "head", "final.norm"};
+  if (e->l_loop_in) n.push_back("loop.in");
+  for (size_t l = 0; l < e->ll.size(); ++l) {
+    const b2_layer_spec& sp = e->ll[l].sp;
+    const std::string p = "l" + std::to_string(l) + ".";
+    n.push_back(p + "norm1");
+    if (sp.mixer == B2_MIXER_WINDOW_AND_STATE) {
+      for (const char* t : {"q", "q.b", "k", "k.b", "v", "v.b", "q.norm", "k.norm", "o", "out"}) n.push_back(p + "mix.left." + t);
+      for (const char* t : {"q", "k", "v", "g", "o", "norm", "a1", "a2", "a2.b", "out"}) n.push_back(p + "mix.right." + t);
+    } else {
+      for (const char* t : {"q", "k", "v", "q.conv", "k.conv", "v.conv", "b", "A_log", "norm", "a1", "a2", "dt_bias", "g1", "g2", "o"}) n.push_back(p + "mix." + t);
+    }
+    if (sp.ff == B2_FF_POLYNORM) {
+      for (const char* t : {"up", "down", "act"}) n.push_back(p + "mlp." + t);
+    } else if (sp.ff == B2_FF_SCALED_GATED_EXPERTS) {
+      n.push_back(p + "mlp.router");
+      for (int x = 0; x < sp.experts; ++x)
+        for (const char* t : {"gate", "up", "down"}) n.push_back(p + "mlp.e" + std::to_string(x) + "." + t);
+      if (sp.shared_ff > 0)
+        for (const char* t : {"gate", "up", "down"}) n.push_back(p + "mlp.shared." + t);
+    }
+  }
+  return n;
+}
+
+// Every tensor is in: the low-rank first stages join the fused projections, and the buffer the projections write is sized.
+int state_finalize(b2_engine* e) {
+  const size_t W = e->cfg.hidden;
+  for (const std::string& name : state_tensor_names(e)) B2_REQUIRE(e->loaded.count(name), "weights incomplete: %s missing", name.c_str());
+  size_t max_nqd = 1;
+  for (size_t l = 0; l < e->ll.size(); ++l) {
+    ListLayer& L = e->ll[l];
+    const b2_layer_spec& sp = L.sp;
+    const bool two = sp.mixer == B2_MIXER_WINDOW_AND_STATE;
+    const size_t dec = two ? (size_t)sp.s_heads * sp.s_dim : (size_t)sp.heads * sp.dim;
+    B2_REQUIRE(L.rank_a >= 1 && L.a2_floats == dec * L.rank_a, "layer %zu: a1 has %d rows, a2 %zu numbers for %zu channels", l, L.rank_a, L.a2_floats, dec);
+    B2_REQUIRE(two || (L.rank_g >= 1 && L.g2_floats == (size_t)sp.heads * sp.vdim * L.rank_g), "layer %zu: g1 has %d rows, g2 %zu numbers", l, L.rank_g,
+               L.g2_floats);
+    if (L.nqd == L.n_fixed) {   // (not yet joined: finalize may be called again after more tensors)
+      const size_t rows = (size_t)L.n_fixed + L.rank_a + L.rank_g;
+      char* fused = nullptr;
+      B2_TRY(dalloc(&fused, rows * W * e->esz));
+      B2_CUDA_OK(cudaMemcpy(fused, L.wqd, (size_t)L.n_fixed * W * e->esz, cudaMemcpyDeviceToDevice));
+      B2_TRY(put_operand(e, fused, (size_t)L.n_fixed * W, L.a1_host.data(), L.a1_host.size()));
+      if (L.rank_g > 0) B2_TRY(put_operand(e, fused, ((size_t)L.n_fixed + L.rank_a) * W, L.g1_host.data(), L.g1_host.size()));
+      cudaFree(L.wqd);
+      L.wqd = fused;
+      L.nqd = (int)rows;
+      e->weight_bytes += (int64_t)((rows - L.n_fixed) * W * e->esz);
+      L.a1_host.clear();
+      L.a1_host.shrink_to_fit();
+      L.g1_host.clear();
+      L.g1_host.shrink_to_fit();
+    }
+    max_nqd = std::max(max_nqd, (size_t)L.nqd);
+  }
+  if (e->l_qd == nullptr || max_nqd > e->l_qd_cols) {
+    if (e->l_qd) cudaFree(e->l_qd);
+    e->l_qd = nullptr;
+    B2_TRY(dalloc(&e->l_qd, (size_t)e->cap_tokens * max_nqd));
+    e->l_qd_cols = max_nqd;
+  }
+  return 0;
+}
+
 // Validates the layer list and allocates weights, activations and scratch of a layer-list engine.
 int list_engine_alloc(b2_engine* e) {
+  if (e->cfg.arch == B2_ARCH_BUMALIX) return state_engine_alloc(e);
   if (e->cfg.arch == B2_ARCH_KEDASUN) return heads_engine_alloc(e);
   const b2_config& c = e->cfg;
   const size_t W = c.hidden, es = e->esz;
@@ -2151,7 +2780,7 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
   B2_REQUIRE(cfg != nullptr && out != nullptr, "b2_engine_create: null argument");
   B2_REQUIRE(cfg->abi_version == B2_ABI_VERSION, "b2_engine_create: abi_version %d != %d", cfg->abi_version, B2_ABI_VERSION);
   B2_REQUIRE(cfg->arch == B2_ARCH_QWEN3 || cfg->arch == B2_ARCH_PHI3 || cfg->arch == B2_ARCH_OPT || list_arch(cfg->arch),
-             "arch %d not built (0 = Qwen3, 1 = Phi-3, 2 = OPT, 3 = Lerasun, 4 = Kedasun)", cfg->arch);
+             "arch %d not built (0 = Qwen3, 1 = Phi-3, 2 = OPT, 3 = Lerasun, 4 = Kedasun, 5 = Bumalix)", cfg->arch);
   const bool ls = list_arch(cfg->arch);  // a layer-list family: its sizes live in layer_specs and are checked in list_engine_alloc
   B2_REQUIRE(ls || !cfg->compute_f32, "compute_f32: only the layer-list families have an fp32 path");
   B2_REQUIRE(!ls || cfg->layer_specs != nullptr, "layer-list family: layer_specs is NULL");
@@ -2416,7 +3045,13 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
       // bytes one page takes in all regions together
       size_t page_bytes_all = blk_elems * 2 * 2 * c.num_layers;
       const bool heads_cache = c.arch == B2_ARCH_KEDASUN;  // a K region and a V region per layer, rows of kv_heads * dim / kv_heads * vdim
-      if (ls) {
+      const bool state_arch = c.arch == B2_ARCH_BUMALIX;   // a K and a V region per RUN of a layer that has a softmax mixer
+      if (state_arch) {
+        page_bytes_all = 0;
+        for (const ListRun& R : e->runs)
+          if (e->ll[R.layer].sp.mixer == B2_MIXER_WINDOW_AND_STATE) page_bytes_all += (size_t)c.block_size * (e->ll[R.layer].nk + e->ll[R.layer].nv) * e->esz;
+        page_bytes_all = std::max<size_t>(page_bytes_all, 16);
+      } else if (ls) {
         page_bytes_all = 0;
         for (const ListLayer& L : e->ll) {
           if (heads_cache) page_bytes_all += (size_t)c.block_size * (L.nk + L.nv) * e->esz;
@@ -2442,7 +3077,21 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
         E_TRY(dalloc(&e->l_pool, (size_t)nb * page_bytes_all));
         E_CUDA(cudaMemset(e->l_pool, 0, (size_t)nb * page_bytes_all));
         size_t off = 0;
+        if (state_arch) {
+          for (ListRun& R : e->runs) {
+            const ListLayer& L = e->ll[R.layer];
+            if (L.sp.mixer != B2_MIXER_WINDOW_AND_STATE) continue;
+            const size_t kb = (size_t)c.block_size * L.nk * e->esz, vb = (size_t)c.block_size * L.nv * e->esz;
+            R.k_region = (int)e->regions.size();
+            e->regions.push_back({e->l_pool + off, kb});
+            off += (size_t)nb * kb;
+            R.v_region = (int)e->regions.size();
+            e->regions.push_back({e->l_pool + off, vb});
+            off += (size_t)nb * vb;
+          }
+        }
         for (ListLayer& L : e->ll) {
+          if (state_arch) break;
           if (heads_cache) {
             const size_t kb = (size_t)c.block_size * L.nk * e->esz, vb = (size_t)c.block_size * L.nv * e->esz;
             L.cache_region = (int)e->regions.size();
@@ -2460,7 +3109,7 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
           off += (size_t)nb * pb;
         }
         for (ListLayer& L : e->ll)
-          if (!heads_cache && L.sp.kv_from >= 0) L.cache_region = e->ll[L.sp.kv_from].cache_region;
+          if (!state_arch && !heads_cache && L.sp.kv_from >= 0) L.cache_region = e->ll[L.sp.kv_from].cache_region;
       } else {
         E_TRY(dalloc(&e->kv_pool, (size_t)2 * c.num_layers * e->layer_kv_elems));
         E_CUDA(cudaMemset(e->kv_pool, 0, (size_t)2 * c.num_layers * e->layer_kv_elems * 2));
@@ -2509,6 +3158,12 @@ extern "C" int b2_engine_load_safetensors(b2_engine* e, const char* path) {
 extern "C" int b2_engine_finalize(b2_engine* e) {
   B2_REQUIRE(e, "b2_engine_finalize: null engine");
   const int arch = e->cfg.arch;
+  if (arch == B2_ARCH_BUMALIX) {
+    B2_CUDA_OK(cudaSetDevice(e->device));
+    B2_TRY(state_finalize(e));
+    e->finalized = true;
+    return 0;
+  }
   if (list_arch(arch)) {
     const int want = list_tensor_count(e);
     int have = 0;
@@ -2567,7 +3222,12 @@ extern "C" void b2_engine_free(b2_engine* e) {
   for (auto& L : e->ll) {
     F(L.wqd); F(L.ukT); F(L.uv); F(L.wo); F(L.up); F(L.down); F(L.gain1); F(L.gain2); F(L.lat_gain); F(L.sink); F(L.router); F(L.corr);
     F(L.gain1b); F(L.gain2b); F(L.qkv_bias); F(L.o_bias); F(L.conv_w); F(L.talk); F(L.vmix); F(L.conv_ring);
+    F(L.wo2); F(L.sh_up); F(L.sh_down); F(L.qk_gain); F(L.head_gain); F(L.a2); F(L.a2_bias); F(L.g2); F(L.a_log); F(L.out_gain_l); F(L.out_gain_r); F(L.poly);
   }
+  for (auto& R : e->runs) {
+    F(R.state); F(R.ring);
+  }
+  F(e->l_loop_in); F(e->l_cat); F(e->l_av2); F(e->l_dec); F(e->l_beta); F(e->l_gate); F(e->l_so); F(e->l_mix2); F(e->l_ffd); F(e->l_slot_scale);
   if (e->ev_fork) cudaEventDestroy(e->ev_fork);
   if (e->ev_join) cudaEventDestroy(e->ev_join);
   if (e->stream2) cudaStreamDestroy(e->stream2);
@@ -2736,7 +3396,7 @@ int prefill_impl(b2_engine* e, const int32_t* ids, const int32_t* seq_offsets, i
   for (int i = 0; i < nseq; ++i) {
     Seq& s = e->seqs[seq_ids[i]];
     const int n = seq_offsets[i + 1] - seq_offsets[i];
-    if (e->prefix_cache && nrows == 0 && s.len == 0 && s.chain_open && s.chain.empty()) {
+    if (e->prefix_cache && !e->l_has_state && nrows == 0 && s.len == 0 && s.chain_open && s.chain.empty()) {   // (state besides the cache cannot be skipped into)
       skip[i] = pc_match(e, s, ids + seq_offsets[i], n);
       s.len = skip[i];  // K/V of those positions are in the pages just taken
       e->pc_queries += n;
@@ -2803,6 +3463,7 @@ int prefill_impl(b2_engine* e, const int32_t* ids, const int32_t* seq_offsets, i
   }
   if (e->debug_flags & 2) B2_TRY(ensure_logits(e));
   e->cur_batch.clear();
+  e->step_portions = nseq;
   B2_TRY(forward(e, T, ntiles, nseq + nrows, 1));
   // the produced tokens become the device-resident "next input" of these sequences
   B2_CUDA_OK(cudaMemcpyAsync(e->h_out, e->d_out_tokens, nseq * 4, cudaMemcpyDeviceToHost, e->stream));
@@ -3069,7 +3730,8 @@ extern "C" int b2_set_debug(b2_engine* e, int32_t flags) {
   if ((flags & 1) && list_arch(e->cfg.arch)) {
     if (e->dbg_hidden_f32 == nullptr) {
       e->dbg_cap_tokens = std::min(e->cap_tokens, 1024);
-      B2_TRY(dalloc(&e->dbg_hidden_f32, (size_t)(e->cfg.num_layers + 1) * e->dbg_cap_tokens * e->cfg.hidden));
+      if (e->dbg_slots <= 0) e->dbg_slots = e->cfg.num_layers + 1;
+      B2_TRY(dalloc(&e->dbg_hidden_f32, (size_t)e->dbg_slots * e->dbg_cap_tokens * e->cfg.hidden));
     }
   } else if ((flags & 1) && e->dbg_hidden == nullptr) {
     e->dbg_cap_tokens = std::min(e->cap_tokens, 1024);
@@ -3096,7 +3758,7 @@ extern "C" int b2_get_hidden(b2_engine* e, int32_t layer, int32_t ntokens, uint1
 extern "C" int b2_get_hidden_f32(b2_engine* e, int32_t layer, int32_t ntokens, float* out_f32) {
   B2_REQUIRE(e && out_f32, "b2_get_hidden_f32: null argument");
   B2_REQUIRE((e->debug_flags & 1) && e->dbg_hidden_f32, "b2_get_hidden_f32: hidden capture not enabled, or the family's residual stream is bf16");
-  B2_REQUIRE(layer >= -1 && layer < e->cfg.num_layers, "b2_get_hidden_f32: layer %d out of range", layer);
+  B2_REQUIRE(layer >= -1 && layer + 1 < e->dbg_slots, "b2_get_hidden_f32: layer %d out of range (a looped layer counts once per pass)", layer);
   B2_REQUIRE(ntokens >= 1 && ntokens <= e->dbg_cap_tokens && ntokens <= e->last_tokens, "b2_get_hidden_f32: ntokens %d out of range", ntokens);
   B2_CUDA_OK(cudaSetDevice(e->device));
   B2_CUDA_OK(cudaStreamSynchronize(e->stream));

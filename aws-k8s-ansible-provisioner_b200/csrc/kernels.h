@@ -265,6 +265,22 @@ int launch_group_norm_add(float* h, const float* y, const float* bias, const flo
 // act[t][i] = g * sigmoid(sharp * g) * (u + 1), g = min(gu[t][i], limit), u = clamp(gu[t][F + i], -limit, limit); gu fp32 [T][2F]
 int launch_clamped_gate(const float* gu, void* act, int act_f32, int T, int F, float limit, float sharp, cudaStream_t s);
 
+// x[t][col0 .. col0 + W) = src[t][0 .. W) in the operand type (x rows of ldx elements): one half of a concatenated projection input
+int launch_store_rows(const float* src, void* x, int x_f32, int ldx, int col0, int T, int W, cudaStream_t s);
+// act[t][i] = a N(z)[i] + b N(z^2)[i] + c N(z^3)[i] + e with N(y) = y / sqrt(mean(y^2) + eps) over the row and powers taken
+// element by element; coef (device) = a, b, c, e; z fp32 [T][F]
+int launch_poly_norm(const float* z, const float* coef, void* act, int act_f32, int T, int F, float eps, cudaStream_t s);
+// act[r][i] = silu(s g) * (s u), g = gu[r][i], u = gu[r][F + i], s = row_scale[row_of ? row_of[r] : r] (null = 1): a gated unit whose INPUT was
+// multiplied by s, applied behind the products; gu fp32 [rows][2F].  row_of maps a row to the entry of row_scale (an expert slot to its pair).
+int launch_silu_gate(const float* gu, const float* row_scale, const int32_t* row_of, void* act, int act_f32, int rows, int F, cudaStream_t s);
+// h[t] += coef * (n(a[t]) * gain_a + n(b[t]) * gain_b) + d1[t] + sum_k y[pair_slot[t * top + k]], n = RMS norm over the row; a null gain
+// adds the branch as it is, null branches are left out.  With gain_next, x_next[t] = n(h[t]) * gain_next follows in the same pass.
+int launch_branch_add(float* h, const float* a, const float* gain_a, const float* b, const float* gain_b, float coef, const float* d1,
+                      const float* y, const int32_t* pair_slot, int top, int T, int W, float eps, cudaStream_t s,
+                      const float* gain_next = nullptr, void* x_next = nullptr, int x_f32 = 0);
+// logits <- cap * tanh(logits / cap), in place
+int launch_softcap(float* logits, size_t n, float cap, cudaStream_t s);
+
 // ---- attn_heads.cu: softmax attention with per-head keys and values, any head width, fp32 or bf16 cache ----
 struct HeadsGeom {
   int heads, kv_heads, dim, vdim;   // query head a reads key/value head a / (heads / kv_heads)
@@ -294,8 +310,46 @@ int launch_heads_attention(const float* q, const void* k_cache, const void* v_ca
                            const int32_t* block_table, int bt_stride, int block_size, const PrefillTile* tiles, int ntiles,
                            const int32_t* positions, const int32_t* seq_lens, void* out, int out_f32, int T, cudaStream_t s);
 // out[t][a][d] = sigmoid(gate[t*gate_ld + a]) * sum_b talk[a][b] * cross[t][b][(a / (heads/kv_heads)) * vdim + d]; gate may be null
+// What follows a fused, biased q | k | v projection when q and k are RMS-normed over the WHOLE row (all heads at once) with a gain per
+// entry: proj [T][ld] fp32 = q (heads*dim) | k (kv_heads*dim) | v (kv_heads*vdim) | anything else; bias [nq + nk + nv] or null;
+// qk_gain [nq + nk].  Writes q_out [T][heads*dim] fp32 and the token's K and V cache rows (plain layout).
+int launch_heads_finish_rownorm(const float* proj, int ld, const HeadsGeom& g, const float* bias, const float* qk_gain, const int32_t* slots,
+                                float* q_out, void* k_cache, void* v_cache, int cache_f32, int T, cudaStream_t s);
 int launch_talk_gate(const float* cross, const float* talk, const float* gate, int gate_ld, void* out, int out_f32, int heads, int kv_heads,
                      int vdim, int T, cudaStream_t s);
+
+// ---- attn_state.cu: mixers with a matrix state per head (gated linear attention, gated delta rule) ----
+enum StateRule { STATE_RULE_DECAY = 0, STATE_RULE_DELTA = 1 };
+struct StateGeom {
+  int heads, kv_heads, dim, vdim;   // state head a reads query/key head a / (heads / kv_heads); S is [dim][vdim] per head
+  int rule;                         // StateRule
+};
+enum LowRankMode {
+  LOWRANK_SIGMOID = 0,              // y = sigmoid(z)
+  LOWRANK_DECAY_SIGMOID_POW = 1,    // y = sigmoid(z)^rate, formed as exp(-rate * softplus(-z))
+  LOWRANK_DECAY_SOFTPLUS = 2        // y = exp(-exp(rate_log[c / per_head]) * softplus(z))
+};
+// out [T][C] fp32 = act(w2 [C][rank] . lr[t][lr_off .. lr_off + rank) + bias [C] (or null))
+int launch_lowrank_act(const float* lr, int ld, int lr_off, int rank, const float* w2, const float* bias, int mode, float rate,
+                       const float* rate_log, int per_head, float* out, int T, int C, cudaStream_t s);
+// Delta rule, behind the fused projection proj [T][ld] fp32 = q (kv_heads*dim) | k (kv_heads*dim) | v (heads*vdim) | beta logits (heads) | ...:
+// causal convolution over time (conv_w [channels][taps], last column = the current token; ring [slots][taps][channels], row = position mod
+// taps) and silu on every channel, q and k heads to unit vectors x / sqrt(sum x^2 + unit_eps), q times dim^-1/2; out [T][channels], beta_out
+// [T][heads] = sigmoid.  Updates the ring.
+int launch_conv_unit_finish(const float* proj, int ld, const StateGeom& g, int taps, const float* conv_w, float* ring, const int32_t* row_seq,
+                            const int32_t* row_first, const int32_t* row_end, const int32_t* positions, const int32_t* slots, float unit_eps,
+                            float* out, float* beta_out, int T, cudaStream_t s);
+// The recurrence over every portion of the step: portion i ends at row last_rows[i] (null: row i is a portion of one token); q / k rows of
+// kv_heads*dim at strides ldq / ldk, v rows of heads*vdim at stride ldv, decay [T][heads*dim], beta [T][heads] (delta rule); q is multiplied
+// by qscale.  state [slots][2][heads][dim][vdim] fp32 (state_floats_per_slot); out [T][heads*vdim] fp32.  Rows whose slot is negative are skipped.
+int launch_state_scan(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* decay, const float* beta,
+                      const StateGeom& g, float qscale, float* state, int portions, const int32_t* last_rows, const int32_t* row_seq,
+                      const int32_t* row_first, const int32_t* row_end, const int32_t* positions, const int32_t* slots, float* out,
+                      cudaStream_t s);
+size_t state_floats_per_slot(const StateGeom& g);
+// out[t][a][:] = o[t][a][:] / sqrt(mean(o[t][a]^2) + eps) * gain[:] * (gate_silu ? silu(gate) : gate), gate at gate[t * gate_ld + a * vdim + :]
+int launch_state_out_gate(const float* o, const float* gain, const float* gate, int gate_ld, int gate_silu, void* out, int out_f32,
+                          int heads, int vdim, float eps, int T, cudaStream_t s);
 
 // ---- attn_latent.cu: attention over a shared per-token latent (absorbed form) ----
 // The cache holds, per token, the normalised latent c [kv_rank] and the rotated key piece [rot_dim] side by side
@@ -322,8 +376,9 @@ size_t latent_attention_scratch_floats(int max_rows, int max_heads, int max_rank
 // ---- moe_route.cu: sigmoid router with a choice offset and grouped selection, and the token permutation by expert ----
 struct RouteGeom {
   int experts, top, groups, keep;
+  int raw_weights;   // 1: the weights are the chosen experts' scores as they are; 0: divided by their sum
 };
-// x [T][W] (operand type), router [experts][W] fp32, correction [experts] fp32 -> idx [T][top], weight [T][top]
+// x [T][W] (operand type), router [experts][W] fp32, correction [experts] fp32 (null = none) -> idx [T][top], weight [T][top]
 int launch_route(const void* x, int x_f32, const float* router, const float* correction, const RouteGeom& g, int32_t* idx, float* weight,
                  int T, int W, cudaStream_t s);
 // counting sort of the T*top (token, choice) pairs by expert: offsets [experts + 1] (the buffer holds 3 * stride ints,
@@ -331,6 +386,8 @@ int launch_route(const void* x, int x_f32, const float* router, const float* cor
 // offsets + 2 * stride; zero it once when it is allocated), slot_token [T*top] (slot -> token), pair_slot [T*top] (pair -> slot).
 int launch_route_permute(const int32_t* idx, int T, int top, int experts, int32_t* offsets, int stride, int32_t* slot_token,
                          int32_t* pair_slot, cudaStream_t s);
+// slot_weight[pair_slot[p]] = weight[p] for the T*top pairs
+int launch_route_slot_weights(const float* weight, const int32_t* pair_slot, float* slot_weight, int npairs, cudaStream_t s);
 // act[i] = bf16(max(up[i], 0)^2), n a multiple of 4
 int launch_relu2_round(const float* up, bf16* act, size_t n, cudaStream_t s);
 // h[t] += sum_k weight[t][k] * y[pair_slot[t*top + k]]   (+ mix[t] when given); fp32

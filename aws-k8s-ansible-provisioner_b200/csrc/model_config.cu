@@ -13,6 +13,13 @@
 //    "layers": [{"type": "attention",   "mixer": {"heads", "kv_heads", "dim", "vdim", "scale", "rot": {"base", "dims"}, "v_mix"?}, "mlp": ...},
 //               {"type": "attention_2", "mixer": {"heads", "kv_heads", "dim", "vdim", "scale", "conv", "mask": {"size", "keep_first"}?, "v_mix"?},
 //                "mlp": null | {"kind": "dense", "ff", "limit"}}, ...]}
+// Bumalix by "architecture": "Bumalix":
+//   {"architecture": "Bumalix", "vocab": V, "width": W, "embedding": {"scale": s}, "norm": {"eps": e}, "logit_softcap": c?,
+//    "loop": {"start", "stop", "times"}?,
+//    "layers": [{"type": "parallel", "mixer": {"left": {"heads", "kv_heads"?, "dim", "vdim", "scale", "mask": {"size"}?},
+//                                              "right": {"heads", "dim", "vdim", "tau"}}, "mlp": ...},
+//               {"type": "channel_delta", "mixer": {"heads", "kv_heads"?, "dim", "vdim", "conv"},
+//                "mlp": null | {"kind": "dense", "ff"} | {"kind": "moe", "expert": {"ff"}, "router": {"experts", "top"}, "shared": {"ff"}?}}, ...]}
 #include <fstream>
 #include <sstream>
 #include <string>
@@ -233,6 +240,132 @@ int kedasun_config(const Value& j, b2_config* c, b2_layer_spec* specs, int max_s
   return 0;
 }
 
+int bumalix_config(const Value& j, b2_config* c, b2_layer_spec* specs, int max_specs) {
+  c->arch = B2_ARCH_BUMALIX;
+  CFG_TRY(need_int(j, "vocab", "config", &c->vocab));
+  CFG_TRY(need_int(j, "width", "config", &c->hidden));
+  const Value* norm = j.find("norm");
+  if (!norm || !norm->is_object()) {
+    b2_set_error("config.json: norm missing");
+    return -22;
+  }
+  CFG_TRY(need_float(*norm, "eps", "norm", &c->rms_eps));
+  c->norm_groups = 1;
+  c->embed_scale = 1.0f;
+  if (const Value* em = j.find("embedding"))
+    if (em->is_object())
+      if (const Value* sc = em->find("scale"))
+        if (sc->is_number()) c->embed_scale = (float)sc->as_double();
+  c->logit_scale = 1.0f;
+  c->logit_softcap = 0.f;
+  if (const Value* cap = j.find("logit_softcap"))
+    if (cap->is_number()) c->logit_softcap = (float)cap->as_double();
+  c->loop_start = c->loop_stop = c->loop_times = 0;
+  if (const Value* loop = j.find("loop"))
+    if (loop->is_object()) {
+      CFG_TRY(need_int(*loop, "start", "loop", &c->loop_start));
+      CFG_TRY(need_int(*loop, "stop", "loop", &c->loop_stop));
+      CFG_TRY(need_int(*loop, "times", "loop", &c->loop_times));
+    }
+  const Value* layers = j.find("layers");
+  if (!layers || !layers->is_array() || layers->size() == 0) {
+    b2_set_error("config.json: layers missing or empty");
+    return -22;
+  }
+  c->num_layers = (int)layers->size();
+  if (c->num_layers > max_specs || specs == nullptr) {
+    b2_set_error("config.json: %d layers, room for %d layer specs", c->num_layers, max_specs);
+    return -22;
+  }
+  if (c->loop_times > 0 && !(c->loop_start >= 0 && c->loop_start <= c->loop_stop && c->loop_stop <= c->num_layers)) {
+    b2_set_error("config.json: loop [%d, %d) outside the %d layers", c->loop_start, c->loop_stop, c->num_layers);
+    return -22;
+  }
+  for (int i = 0; i < c->num_layers; ++i) {
+    const Value& L = layers->at(i);
+    b2_layer_spec& s = specs[i];
+    memset(&s, 0, sizeof s);
+    s.kv_from = -1;
+    char where[64];
+    snprintf(where, sizeof where, "layers[%d].mixer", i);
+    const Value* type = L.find("type");
+    const Value* m = L.find("mixer");
+    if (!type || !type->is_string() || !m || !m->is_object()) {
+      b2_set_error("config.json: layers[%d] needs type and mixer", i);
+      return -22;
+    }
+    if (type->as_string() == "parallel") {
+      s.mixer = B2_MIXER_WINDOW_AND_STATE;
+      const Value* a = m->find("left");
+      const Value* b = m->find("right");
+      if (!a || !a->is_object() || !b || !b->is_object()) {
+        b2_set_error("config.json: %s needs left and right", where);
+        return -22;
+      }
+      snprintf(where, sizeof where, "layers[%d].mixer.left", i);
+      CFG_TRY(need_int(*a, "heads", where, &s.heads));
+      s.kv_heads = s.heads;
+      if (const Value* kh = a->find("kv_heads"))
+        if (kh->is_number()) s.kv_heads = (int)kh->as_int();
+      CFG_TRY(need_int(*a, "dim", where, &s.dim));
+      CFG_TRY(need_int(*a, "vdim", where, &s.vdim));
+      CFG_TRY(need_float(*a, "scale", where, &s.scale));
+      const Value* mask = a->find("mask");
+      if (mask && mask->is_object()) CFG_TRY(need_int(*mask, "size", where, &s.window));  // no "mask": every earlier key is seen
+      snprintf(where, sizeof where, "layers[%d].mixer.right", i);
+      CFG_TRY(need_int(*b, "heads", where, &s.s_heads));
+      CFG_TRY(need_int(*b, "dim", where, &s.s_dim));
+      CFG_TRY(need_int(*b, "vdim", where, &s.s_vdim));
+      CFG_TRY(need_float(*b, "tau", where, &s.s_tau));
+    } else if (type->as_string() == "channel_delta") {
+      s.mixer = B2_MIXER_DELTA_STATE;
+      CFG_TRY(need_int(*m, "heads", where, &s.heads));
+      s.kv_heads = s.heads;
+      if (const Value* kh = m->find("kv_heads"))
+        if (kh->is_number()) s.kv_heads = (int)kh->as_int();
+      CFG_TRY(need_int(*m, "dim", where, &s.dim));
+      CFG_TRY(need_int(*m, "vdim", where, &s.vdim));
+      CFG_TRY(need_int(*m, "conv", where, &s.conv_taps));
+    } else {
+      b2_set_error("config.json: layers[%d]: mixer type '%s' not built (parallel, channel_delta)", i, type->as_string().c_str());
+      return -22;
+    }
+    const Value* mlp = L.find("mlp");
+    s.ff = B2_FF_NONE;
+    if (mlp && mlp->is_object()) {
+      snprintf(where, sizeof where, "layers[%d].mlp", i);
+      const Value* kind = mlp->find("kind");
+      const std::string kd = kind && kind->is_string() ? kind->as_string() : "?";
+      if (kd == "dense") {
+        s.ff = B2_FF_POLYNORM;
+        CFG_TRY(need_int(*mlp, "ff", where, &s.ff_dim));
+      } else if (kd == "moe") {
+        s.ff = B2_FF_SCALED_GATED_EXPERTS;
+        const Value* ex = mlp->find("expert");
+        const Value* ro = mlp->find("router");
+        if (!ex || !ex->is_object() || !ro || !ro->is_object()) {
+          b2_set_error("config.json: %s needs expert and router", where);
+          return -22;
+        }
+        CFG_TRY(need_int(*ex, "ff", where, &s.ff_dim));
+        CFG_TRY(need_int(*ro, "experts", where, &s.experts));
+        CFG_TRY(need_int(*ro, "top", where, &s.top));
+        s.groups = s.groups_keep = 1;
+        if (const Value* sh = mlp->find("shared"))
+          if (sh->is_object()) CFG_TRY(need_int(*sh, "ff", where, &s.shared_ff));
+      } else {
+        b2_set_error("config.json: %s.kind '%s' not built (dense, moe)", where, kd.c_str());
+        return -22;
+      }
+    }
+  }
+  c->layer_specs = specs;
+  c->tie_embeddings = 0;
+  c->num_q_heads = c->num_kv_heads = 0;
+  c->head_dim = c->intermediate = 0;
+  return 0;
+}
+
 }  // namespace
 
 extern "C" int b2_config_from_dir(const char* model_dir, b2_config* c, b2_layer_spec* specs, int32_t max_specs) {
@@ -257,10 +390,13 @@ extern "C" int b2_config_from_dir(const char* model_dir, b2_config* c, b2_layer_
   c->logit_scale = 0.f;
   c->embed_scale = 0.f;
   c->norm_groups = 0;
+  c->loop_start = c->loop_stop = c->loop_times = 0;
+  c->logit_softcap = 0.f;
   const Value* archv = j.find("architecture");
   if (archv && archv->is_string()) {
     if (archv->as_string() == "Lerasun") return lerasun_config(j, c, specs, max_specs);
     if (archv->as_string() == "Kedasun") return kedasun_config(j, c, specs, max_specs);
+    if (archv->as_string() == "Bumalix") return bumalix_config(j, c, specs, max_specs);
     b2_set_error("%s: architecture '%s' not built", path.c_str(), archv->as_string().c_str());
     return -22;
   }

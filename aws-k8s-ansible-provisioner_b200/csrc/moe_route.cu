@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restri
     if (lane == 0) {
       const float sg = 1.0f / (1.0f + expf(-acc));
       s[e] = sg;
-      ch[e] = sg + correction[e];
+      ch[e] = sg + (correction ? correction[e] : 0.f);
     }
   }
   __syncthreads();
@@ -99,6 +99,7 @@ __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restri
     sum += s[best];
     ch[best] = -INFINITY;
   }
+  if (g.raw_weights) return;   // the scores as they are
   const float inv = 1.0f / (sum + 1e-20f);
   for (int k = 0; k < g.top; ++k) weight[(size_t)t * g.top + k] *= inv;
 }
@@ -209,6 +210,15 @@ __global__ void __launch_bounds__(256) route_combine_kernel(float* __restrict__ 
   }
 }
 
+// slot_weight[pair_slot[p]] = weight[p]: the pairs' weights in expert (slot) order, for experts whose INPUT the weight multiplies
+__global__ void __launch_bounds__(256) route_slot_weights_kernel(const float* __restrict__ weight, const int32_t* __restrict__ pair_slot,
+                                                                 float* __restrict__ slot_weight, int npairs) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int p = blockIdx.x * 256 + threadIdx.x;
+  if (p < npairs) slot_weight[pair_slot[p]] = weight[p];
+}
+
 // act = bf16(max(up, 0)^2): the experts' activation between the two dense products of a prompt-sized step
 __global__ void __launch_bounds__(256) relu2_round_kernel(const float4* __restrict__ up, uint2* __restrict__ act, size_t n4) {
   pdl_wait();
@@ -268,6 +278,12 @@ int launch_route_permute(const int32_t* idx, int T, int top, int experts, int32_
   B2_CUDA_OK(b2_launch(route_count_kernel, dim3((npairs + 255) / 256), dim3(256), (size_t)experts * sizeof(int), s, idx, npairs, experts, counts));
   B2_CUDA_OK(b2_launch(route_scan_kernel, dim3(1), dim3(32), 0, s, counts, experts, offsets, cursor));
   B2_CUDA_OK(b2_launch(route_place_kernel, dim3((npairs + 255) / 256), dim3(256), 0, s, idx, npairs, top, cursor, slot_token, pair_slot));
+  return 0;
+}
+
+int launch_route_slot_weights(const float* weight, const int32_t* pair_slot, float* slot_weight, int npairs, cudaStream_t s) {
+  if (npairs <= 0) return 0;
+  B2_CUDA_OK(b2_launch(route_slot_weights_kernel, dim3((npairs + 255) / 256), dim3(256), 0, s, weight, pair_slot, slot_weight, npairs));
   return 0;
 }
 

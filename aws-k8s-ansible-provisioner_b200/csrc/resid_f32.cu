@@ -242,6 +242,111 @@ __global__ void __launch_bounds__(256) clamped_gate_kernel(const float* __restri
   }
 }
 
+// ---- a parallel layer with ONE norm and several branches (Bumalix) ----
+template <typename TX>
+__global__ void __launch_bounds__(256) store_rows_kernel(const float* __restrict__ src, TX* __restrict__ x, int ldx, int col0, int W) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += 256) x[(size_t)t * ldx + col0 + i] = (TX)src[(size_t)t * W + i];
+}
+
+// One CTA of 128 threads per token row: three power sums in one pass, then the polynomial of the three unit-RMS vectors.
+template <typename TX>
+__global__ void __launch_bounds__(128) poly_norm_kernel(const float* __restrict__ z, const float* __restrict__ coef, TX* __restrict__ act, int F,
+                                                        float eps) {
+  __shared__ float red[4];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const float* row = z + (size_t)t * F;
+  float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+  for (int i = threadIdx.x; i < F; i += 128) {
+    const float v = row[i], v2 = v * v, v3 = v2 * v;
+    s2 = fmaf(v, v, s2);
+    s4 = fmaf(v2, v2, s4);
+    s6 = fmaf(v3, v3, s6);
+  }
+  s2 = block_sum_128(s2, red);
+  s4 = block_sum_128(s4, red);
+  s6 = block_sum_128(s6, red);
+  const float r1 = coef[0] / sqrtf(s2 / (float)F + eps), r2 = coef[1] / sqrtf(s4 / (float)F + eps), r3 = coef[2] / sqrtf(s6 / (float)F + eps);
+  const float e = coef[3];
+  for (int i = threadIdx.x; i < F; i += 128) {
+    const float v = row[i], v2 = v * v;
+    act[(size_t)t * F + i] = (TX)(r1 * v + r2 * v2 + r3 * (v2 * v) + e);
+  }
+}
+
+template <typename TX>
+__global__ void __launch_bounds__(256) silu_gate_kernel(const float* __restrict__ gu, const float* __restrict__ row_scale,
+                                                        const int32_t* __restrict__ row_of, TX* __restrict__ act, int F) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  const float sc = row_scale ? row_scale[row_of ? row_of[r] : r] : 1.0f;
+  const float* row = gu + (size_t)r * 2 * F;
+  for (int i = blockIdx.y * 256 + threadIdx.x; i < F; i += 256 * gridDim.y) {
+    const float g = sc * row[i], u = sc * row[F + i];
+    act[(size_t)r * F + i] = (TX)(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+// h[t] += coef * (n(a) ga + n(b) gb) + d1 + sum_k y[slot_k]; then optionally x_next = n(h) * gain_next.  One CTA per row.
+constexpr int BA_MAX_TOP = 16;
+template <typename TX>
+__global__ void __launch_bounds__(128) branch_add_kernel(float* __restrict__ h, const float* __restrict__ a, const float* __restrict__ gain_a,
+                                                         const float* __restrict__ b, const float* __restrict__ gain_b, float coef,
+                                                         const float* __restrict__ d1, const float* __restrict__ y,
+                                                         const int32_t* __restrict__ pair_slot, int top, int W, float eps,
+                                                         const float* __restrict__ gain_next, TX* __restrict__ x_next) {
+  __shared__ float red[4];
+  __shared__ int slot_s[BA_MAX_TOP];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const float* ar = a ? a + (size_t)t * W : nullptr;
+  const float* br = b ? b + (size_t)t * W : nullptr;
+  const float* dr = d1 ? d1 + (size_t)t * W : nullptr;
+  float* hr = h + (size_t)t * W;
+  if (y != nullptr && (int)threadIdx.x < min(top, BA_MAX_TOP)) slot_s[threadIdx.x] = pair_slot[(size_t)t * top + threadIdx.x];
+  float ra = 1.0f, rb = 1.0f;
+  if (ar && gain_a) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < W; i += 128) ss = fmaf(ar[i], ar[i], ss);
+    ra = 1.0f / sqrtf(block_sum_128(ss, red) / (float)W + eps);
+  }
+  if (br && gain_b) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < W; i += 128) ss = fmaf(br[i], br[i], ss);
+    rb = 1.0f / sqrtf(block_sum_128(ss, red) / (float)W + eps);
+  }
+  __syncthreads();
+  float ss2 = 0.f;
+  for (int i = threadIdx.x; i < W; i += 128) {
+    float m = 0.f;
+    if (ar) m = ar[i] * ra * (gain_a ? gain_a[i] : 1.0f);
+    if (br) m += br[i] * rb * (gain_b ? gain_b[i] : 1.0f);
+    m *= coef;
+    float ff = dr ? dr[i] : 0.f;
+    if (y != nullptr)
+      for (int k = 0; k < top; ++k) ff += y[(size_t)(k < BA_MAX_TOP ? slot_s[k] : pair_slot[(size_t)t * top + k]) * W + i];   // choice order
+    const float hn = hr[i] + (m + ff);
+    hr[i] = hn;
+    ss2 = fmaf(hn, hn, ss2);
+  }
+  if (gain_next != nullptr) {
+    const float r2 = 1.0f / sqrtf(block_sum_128(ss2, red) / (float)W + eps);
+    for (int i = threadIdx.x; i < W; i += 128) x_next[(size_t)t * W + i] = (TX)(hr[i] * r2 * gain_next[i]);   // its own writes
+  }
+}
+
+__global__ void __launch_bounds__(256) softcap_kernel(float* __restrict__ logits, size_t n, float cap) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) logits[i] = cap * tanhf(logits[i] / cap);
+}
+
 }  // namespace
 
 constexpr int GN_EARLY_ROWS = 1024;
@@ -312,6 +417,48 @@ int launch_unit_norm2(const float* h, const float* gain_a, const float* gain_b, 
 int launch_logits_finish(const float* logits, int32_t* out_tokens, bf16* logits_bf16, int bf16_rows, int rows, int V, int v_pad, cudaStream_t s) {
   if (rows <= 0) return 0;
   B2_CUDA_OK(b2_launch(logits_finish_kernel, dim3(rows), dim3(1024), 0, s, logits, out_tokens, logits_bf16, bf16_rows, V, v_pad));
+  return 0;
+}
+
+int launch_store_rows(const float* src, void* x, int x_f32, int ldx, int col0, int T, int W, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (x_f32) B2_CUDA_OK(b2_launch(store_rows_kernel<float>, dim3(T), dim3(256), 0, s, src, (float*)x, ldx, col0, W));
+  else B2_CUDA_OK(b2_launch(store_rows_kernel<bf16>, dim3(T), dim3(256), 0, s, src, (bf16*)x, ldx, col0, W));
+  return 0;
+}
+
+int launch_poly_norm(const float* z, const float* coef, void* act, int act_f32, int T, int F, float eps, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (act_f32) B2_CUDA_OK(b2_launch(poly_norm_kernel<float>, dim3(T), dim3(128), 0, s, z, coef, (float*)act, F, eps));
+  else B2_CUDA_OK(b2_launch(poly_norm_kernel<bf16>, dim3(T), dim3(128), 0, s, z, coef, (bf16*)act, F, eps));
+  return 0;
+}
+
+int launch_silu_gate(const float* gu, const float* row_scale, const int32_t* row_of, void* act, int act_f32, int rows, int F, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  const dim3 grid(rows, rows >= 1024 ? 1 : std::max(1, std::min((F + 255) / 256, 1024 / rows)));
+  if (act_f32) B2_CUDA_OK(b2_launch(silu_gate_kernel<float>, grid, dim3(256), 0, s, gu, row_scale, row_of, (float*)act, F));
+  else B2_CUDA_OK(b2_launch(silu_gate_kernel<bf16>, grid, dim3(256), 0, s, gu, row_scale, row_of, (bf16*)act, F));
+  return 0;
+}
+
+int launch_branch_add(float* h, const float* a, const float* gain_a, const float* b, const float* gain_b, float coef, const float* d1,
+                      const float* y, const int32_t* pair_slot, int top, int T, int W, float eps, cudaStream_t s, const float* gain_next,
+                      void* x_next, int x_f32) {
+  if (T <= 0) return 0;
+  B2_REQUIRE((gain_next == nullptr) == (x_next == nullptr), "branch_add: the following norm needs its gain and its output");
+  B2_REQUIRE(y == nullptr || (pair_slot != nullptr && top >= 1), "branch_add: routed rows need their slots");
+  if (x_f32 || x_next == nullptr)
+    B2_CUDA_OK(b2_launch(branch_add_kernel<float>, dim3(T), dim3(128), 0, s, h, a, gain_a, b, gain_b, coef, d1, y, pair_slot, top, W, eps, gain_next, (float*)x_next));
+  else
+    B2_CUDA_OK(b2_launch(branch_add_kernel<bf16>, dim3(T), dim3(128), 0, s, h, a, gain_a, b, gain_b, coef, d1, y, pair_slot, top, W, eps, gain_next, (bf16*)x_next));
+  return 0;
+}
+
+int launch_softcap(float* logits, size_t n, float cap, cudaStream_t s) {
+  if (n == 0 || !(cap > 0.f)) return 0;
+  const unsigned blocks = (unsigned)std::min<size_t>((n + 255) / 256, 4096);
+  B2_CUDA_OK(b2_launch(softcap_kernel, dim3(blocks), dim3(256), 0, s, logits, n, cap));
   return 0;
 }
 

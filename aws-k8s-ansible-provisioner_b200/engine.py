@@ -46,6 +46,8 @@ class EngineConfig:
     logit_scale: float = 0.0     # lm_head output multiplier (0 = 1)
     embed_scale: float = 0.0     # embedding multiplier (0 = 1)
     norm_groups: int = 0         # Kedasun: pieces of every norm (0 = 1)
+    loop: tuple = (0, 0, 0)      # Bumalix: layers [start, stop) run `times` times in a row (times 0 = no loop)
+    logit_softcap: float = 0.0   # logits <- cap * tanh(logits / cap) (0 = none)
 
     @staticmethod
     def lerasun(model_cfg: dict, **runtime) -> "EngineConfig":
@@ -63,6 +65,16 @@ class EngineConfig:
                             embed_scale=model_cfg.get("embedding", {}).get("scale", 1.0), logit_scale=1.0, arch="kedasun",
                             layers=model_cfg["layers"], tie_embeddings=False, num_q_heads=0, num_kv_heads=0, head_dim=0,
                             intermediate=0, **runtime)
+
+    @staticmethod
+    def bumalix(model_cfg: dict, **runtime) -> "EngineConfig":
+        """From the dict a Bumalix config.json holds (width, vocab, embedding.scale, norm.eps, loop, logit_softcap, layers) plus runtime sizing."""
+        lp = model_cfg.get("loop") or {}
+        return EngineConfig(num_layers=len(model_cfg["layers"]), hidden=model_cfg["width"], vocab=model_cfg["vocab"],
+                            rms_eps=model_cfg["norm"]["eps"], embed_scale=model_cfg.get("embedding", {}).get("scale", 1.0), logit_scale=1.0,
+                            arch="bumalix", layers=model_cfg["layers"], tie_embeddings=False, num_q_heads=0, num_kv_heads=0, head_dim=0,
+                            intermediate=0, loop=(int(lp.get("start", 0)), int(lp.get("stop", 0)), int(lp.get("times", 0))),
+                            logit_softcap=float(model_cfg.get("logit_softcap") or 0.0), **runtime)
 
     def kv_bytes_per_token(self) -> int:
         return 2 * self.num_layers * self.num_kv_heads * self.head_dim * 2
@@ -102,7 +114,9 @@ class Engine:
         c.rope_theta = cfg.rope_theta
         c.gpu_mem_fraction = cfg.gpu_mem_fraction
         c.arch = {"qwen3": capi.ARCH_QWEN3, "phi3": capi.ARCH_PHI3, "opt": capi.ARCH_OPT, "lerasun": capi.ARCH_LERASUN,
-                  "kedasun": capi.ARCH_KEDASUN}[cfg.arch]
+                  "kedasun": capi.ARCH_KEDASUN, "bumalix": capi.ARCH_BUMALIX}[cfg.arch]
+        c.loop_start, c.loop_stop, c.loop_times = (int(v) for v in cfg.loop)
+        c.logit_softcap = float(cfg.logit_softcap)
         c.compute_f32 = int(cfg.compute_f32)
         c.logit_scale = float(cfg.logit_scale)
         c.embed_scale = float(cfg.embed_scale)
@@ -138,16 +152,17 @@ class Engine:
         specs = (b2_layer_spec * 1024)()
         check(lib.b2_config_from_dir(model_dir.encode(), C.byref(c), specs, 1024), lib)
         arch = {capi.ARCH_QWEN3: "qwen3", capi.ARCH_PHI3: "phi3", capi.ARCH_OPT: "opt", capi.ARCH_LERASUN: "lerasun",
-                capi.ARCH_KEDASUN: "kedasun"}[c.arch]
+                capi.ARCH_KEDASUN: "kedasun", capi.ARCH_BUMALIX: "bumalix"}[c.arch]
         layers = None
-        if arch in ("lerasun", "kedasun"):
+        if arch in ("lerasun", "kedasun", "bumalix"):
             layers = [_layer_dict(specs[i]) for i in range(c.num_layers)]
         cfg = EngineConfig(num_layers=c.num_layers, hidden=c.hidden, num_q_heads=c.num_q_heads, num_kv_heads=c.num_kv_heads,
                            head_dim=c.head_dim, intermediate=c.intermediate, vocab=c.vocab, tie_embeddings=bool(c.tie_embeddings),
                            rms_eps=c.rms_eps, rope_theta=c.rope_theta, arch=arch, rotary_dim=c.rotary_dim,
                            max_positions=c.max_positions, sliding_window=c.sliding_window, layers=layers,
                            compute_f32=(dtype == "float32"), logit_scale=c.logit_scale, embed_scale=c.embed_scale,
-                           norm_groups=c.norm_groups, **runtime)
+                           norm_groups=c.norm_groups, loop=(c.loop_start, c.loop_stop, c.loop_times), logit_softcap=c.logit_softcap,
+                           **runtime)
         return cls(cfg, device=device, safetensors_path=os.path.join(model_dir, "model.safetensors"))
 
     # ---- weights -----------------------------------------------------------------------
@@ -320,6 +335,8 @@ def _fill_layer_spec(sp, layer: dict) -> None:
     """One "layers" entry of a layer-list config.json -> b2_layer_spec (the C registry does the same for a directory)."""
     if layer["type"] in ("attention", "attention_2"):
         return _fill_heads_spec(sp, layer)
+    if layer["type"] in ("parallel", "channel_delta"):
+        return _fill_state_spec(sp, layer)
     if layer["type"] != "latent_attention":
         raise B2Error("mixer type %r not built" % layer["type"])
     m = layer["mixer"]
@@ -337,6 +354,34 @@ def _fill_layer_spec(sp, layer: dict) -> None:
         g = r.get("groups") or {"count": 1, "keep": 1}
         sp.ff, sp.ff_dim, sp.experts, sp.top = capi.FF_ROUTED_EXPERTS, int(mlp["expert"]["ff"]), int(r["experts"]), int(r["top"])
         sp.groups, sp.groups_keep = int(g["count"]), int(g["keep"])
+
+
+def _fill_state_spec(sp, layer: dict) -> None:
+    """Bumalix: "parallel" (windowed softmax attention beside gated linear attention) and "channel_delta" (gated delta rule)."""
+    m = layer["mixer"]
+    sp.kv_from = -1
+    if layer["type"] == "parallel":
+        a, b = m["left"], m["right"]
+        sp.mixer = capi.MIXER_WINDOW_AND_STATE
+        sp.heads, sp.kv_heads, sp.dim, sp.vdim = int(a["heads"]), int(a.get("kv_heads", a["heads"])), int(a["dim"]), int(a["vdim"])
+        sp.scale = float(a["scale"])
+        sp.window = int(a["mask"]["size"]) if a.get("mask") else 0
+        sp.s_heads, sp.s_dim, sp.s_vdim, sp.s_tau = int(b["heads"]), int(b["dim"]), int(b["vdim"]), float(b["tau"])
+    else:
+        sp.mixer = capi.MIXER_DELTA_STATE
+        sp.heads, sp.kv_heads, sp.dim, sp.vdim = int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"]), int(m["vdim"])
+        sp.conv_taps = int(m["conv"])
+    mlp = layer.get("mlp")
+    sp.ff = capi.FF_NONE
+    if mlp is not None:
+        if mlp["kind"] == "dense":
+            sp.ff, sp.ff_dim = capi.FF_POLYNORM, int(mlp["ff"])
+        elif mlp["kind"] == "moe":
+            sp.ff, sp.ff_dim = capi.FF_SCALED_GATED_EXPERTS, int(mlp["expert"]["ff"])
+            sp.experts, sp.top, sp.groups, sp.groups_keep = int(mlp["router"]["experts"]), int(mlp["router"]["top"]), 1, 1
+            sp.shared_ff = int(mlp["shared"]["ff"]) if mlp.get("shared") else 0
+        else:
+            raise B2Error("feed-forward kind %r not built" % mlp["kind"])
 
 
 def _fill_heads_spec(sp, layer: dict) -> None:
@@ -364,6 +409,22 @@ def _fill_heads_spec(sp, layer: dict) -> None:
 
 
 def _layer_dict(sp) -> dict:
+    if sp.mixer in (capi.MIXER_WINDOW_AND_STATE, capi.MIXER_DELTA_STATE):
+        if sp.mixer == capi.MIXER_WINDOW_AND_STATE:
+            left = {"heads": sp.heads, "kv_heads": sp.kv_heads, "dim": sp.dim, "vdim": sp.vdim, "scale": sp.scale}
+            if sp.window > 0:
+                left["mask"] = {"size": sp.window}
+            m = {"left": left, "right": {"heads": sp.s_heads, "dim": sp.s_dim, "vdim": sp.s_vdim, "tau": sp.s_tau}}
+        else:
+            m = {"heads": sp.heads, "kv_heads": sp.kv_heads, "dim": sp.dim, "vdim": sp.vdim, "conv": sp.conv_taps}
+        mlp = None
+        if sp.ff == capi.FF_POLYNORM:
+            mlp = {"kind": "dense", "ff": sp.ff_dim}
+        elif sp.ff == capi.FF_SCALED_GATED_EXPERTS:
+            mlp = {"kind": "moe", "expert": {"ff": sp.ff_dim}, "router": {"experts": sp.experts, "top": sp.top}}
+            if sp.shared_ff > 0:
+                mlp["shared"] = {"ff": sp.shared_ff}
+        return {"type": "parallel" if sp.mixer == capi.MIXER_WINDOW_AND_STATE else "channel_delta", "mixer": m, "mlp": mlp}
     if sp.mixer in (capi.MIXER_ATTENTION, capi.MIXER_CONV_ATTENTION):
         m = {"heads": sp.heads, "kv_heads": sp.kv_heads, "dim": sp.dim, "vdim": sp.vdim, "scale": sp.scale, "v_mix": bool(sp.v_mix)}
         if sp.mixer == capi.MIXER_CONV_ATTENTION:

@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define B2_ABI_VERSION 4
+#define B2_ABI_VERSION 5
 
 typedef struct b2_engine b2_engine;
 
@@ -38,11 +38,21 @@ enum b2_mixer_kind {
   B2_MIXER_CONV_ATTENTION = 3    /* biased projections, a short causal convolution on q / k / v, unit-RMS q and k, a linear distance penalty,
                                     a window that keeps the first tokens, mixing of the heads' softmax weights, an output gate (Kedasun
                                     "attention_2") */
+  ,
+  B2_MIXER_WINDOW_AND_STATE = 4, /* two mixers side by side on the same input, each output RMS-normed over the model width, half their sum
+                                    (Bumalix "parallel"): grouped-query softmax attention with biased projections, whole-row RMS norms of q
+                                    and k, no positions, a sliding window; and gated linear attention, a matrix state per head with a decay
+                                    per key channel (s_heads, s_dim, s_vdim, s_tau) */
+  B2_MIXER_DELTA_STATE = 5       /* gated delta rule: a matrix state per head, short causal convolutions on q / k / v, unit-vector q and k,
+                                    a decay per head and key channel, a step size per head, a low-rank output gate (Bumalix "channel_delta") */
 };
 enum b2_ff_kind {
   B2_FF_NONE = 0,
   B2_FF_ROUTED_EXPERTS = 1,
-  B2_FF_CLAMPED_GATED = 2        /* y = g sigmoid(1.702 g) (u + 1), g = min(W_g x, limit), u = clamp(W_u x, -limit, limit); out = W_d y */
+  B2_FF_CLAMPED_GATED = 2,       /* y = g sigmoid(1.702 g) (u + 1), g = min(W_g x, limit), u = clamp(W_u x, -limit, limit); out = W_d y */
+  B2_FF_POLYNORM = 3,            /* W_d p(W_u x), p(z) = a N(z) + b N(z^2) + c N(z^3) + e, N = division by the root mean square over the ff values */
+  B2_FF_SCALED_GATED_EXPERTS = 4 /* sigmoid router, the `top` largest scores; expert = W_d (silu(W_g y) * (W_u y)) on y = score * x (scores not
+                                    renormalised); a shared expert of the same form (shared_ff) on x itself is added */
 };
 typedef struct b2_layer_spec {
   int32_t mixer;        /* b2_mixer_kind */
@@ -69,6 +79,13 @@ typedef struct b2_layer_spec {
   int32_t keep_first;   /* the first keep_first tokens stay visible whatever the window */
   int32_t v_mix;        /* 1: the layer takes part in value mixing (the first such layer supplies, the others blend) */
   float   ff_limit;     /* B2_FF_CLAMPED_GATED: the clamp */
+  /* ABI 5: mixers with a matrix state.  B2_MIXER_WINDOW_AND_STATE: heads / kv_heads / dim / vdim / scale / window describe the softmax half,
+   * s_* the state half.  B2_MIXER_DELTA_STATE: heads (value heads) / kv_heads (query/key heads) / dim / vdim / conv_taps. */
+  int32_t s_heads;      /* state heads of the second mixer */
+  int32_t s_dim;        /* its query/key width per head */
+  int32_t s_vdim;       /* its value width per head */
+  float   s_tau;        /* its decay is sigmoid(.)^(1 / s_tau) */
+  int32_t shared_ff;    /* B2_FF_SCALED_GATED_EXPERTS: inner width of the shared expert (0 = none) */
 } b2_layer_spec;
 
 /* Architecture + runtime sizing.  Field meanings follow HF Qwen3Config
@@ -107,6 +124,11 @@ typedef struct b2_config {
   /* ABI 4 */
   float   embed_scale;       /* the embedding row is multiplied by this (0 = 1; Kedasun) */
   int32_t norm_groups;       /* Kedasun: every norm splits its vector into this many equal pieces with a statistic each (0 = 1) */
+  /* ABI 5 */
+  int32_t loop_start;        /* layers [loop_start, loop_stop) run loop_times times in a row with the same weights, each pass with a cache and */
+  int32_t loop_stop;         /* state of its own; in front of every pass the stream becomes W_in [x; x0], x0 the embedding output */
+  int32_t loop_times;        /* 0 = no loop (and no W_in) */
+  float   logit_softcap;     /* logits <- cap * tanh(logits / cap) (0 = none) */
 } b2_config;
 
 /* Model families.  QWEN3: HF:models/qwen3/modeling_qwen3.py (QK-norm, separate q/k/v and gate/up
@@ -128,11 +150,17 @@ typedef struct b2_config {
  * is an RMS norm over norm_groups pieces with a plain gain; the embedding is scaled by embed_scale.  Mixers: B2_MIXER_ATTENTION and
  * B2_MIXER_CONV_ATTENTION; feed-forward: B2_FF_CLAMPED_GATED or none.  Tensor names: embed, l<i>.norm1|norm1b|norm2|norm2b,
  * l<i>.mix.{q,k,v,o,vmix} (+ .b biases, {q,k,v}.conv, talk, g for the convolution mixer), l<i>.mlp.{gate,up,down}, final.norm, head. */
-enum b2_arch { B2_ARCH_QWEN3 = 0, B2_ARCH_PHI3 = 1, B2_ARCH_OPT = 2, B2_ARCH_LERASUN = 3, B2_ARCH_KEDASUN = 4 };
+/* BUMALIX: a layer list as well.  n = norm1(h); h <- h + (mixer(n) + ff(n)) on an fp32 residual stream, ONE plain-gain RMS norm per layer;
+ * the embedding is scaled by embed_scale; an optional loop over a run of layers (loop_*); logits capped by logit_softcap.  Mixers:
+ * B2_MIXER_WINDOW_AND_STATE and B2_MIXER_DELTA_STATE; feed-forwards: B2_FF_POLYNORM, B2_FF_SCALED_GATED_EXPERTS or none.  Tensor names: embed,
+ * loop.in, l<i>.norm1, l<i>.mix.left.{q,k,v (+ .b), q.norm, k.norm, o, out}, l<i>.mix.right.{q,k,v,g,o,norm,a1,a2,a2.b,out},
+ * l<i>.mix.{q,k,v (+ .conv), b, A_log, a1, a2, dt_bias, g1, g2, norm, o}, l<i>.mlp.{up,down,act} or l<i>.mlp.{router, e<k>.{gate,up,down},
+ * shared.{gate,up,down}}, final.norm, head.  The low-rank widths (a1, g1) are taken from the tensors. */
+enum b2_arch { B2_ARCH_QWEN3 = 0, B2_ARCH_PHI3 = 1, B2_ARCH_OPT = 2, B2_ARCH_LERASUN = 3, B2_ARCH_KEDASUN = 4, B2_ARCH_BUMALIX = 5 };
 
 /* Model registry: reads MODEL_DIR/config.json and fills the architecture fields of *cfg (the runtime sizing fields --
  * max_model_len, block_size, num_blocks, max_seqs, max_batch_tokens, use_cuda_graphs, compute_f32 -- are left as the caller
- * set them).  HF configs are told apart by "model_type" (qwen3, phi3, opt); a config with "architecture": "Lerasun" or "Kedasun" fills
+ * set them).  HF configs are told apart by "model_type" (qwen3, phi3, opt); a config with "architecture": "Lerasun", "Kedasun" or "Bumalix" fills
  * specs[0 .. num_layers) as well and points cfg->layer_specs at it (max_specs = capacity of specs; may be 0 / NULL for the
  * HF families).  Returns 0, or a negative code with b2_last_error(). */
 int  b2_config_from_dir(const char* model_dir, b2_config* cfg, b2_layer_spec* specs, int32_t max_specs);
