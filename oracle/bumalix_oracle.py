@@ -243,6 +243,17 @@ class Stepper:
         return cap * torch.tanh(y / cap) if cap else y
 
 
+    def greedy(self, prompt, n: int):
+        """Feeds the prompt, then n times the most likely token (lowest index on ties); returns the n tokens."""
+        for t in prompt:
+            y = self.step(int(t))
+        out = []
+        for _ in range(n):
+            out.append(int(torch.argmax(y)))
+            y = self.step(out[-1])
+        return out
+
+
 def forward(cfg: dict, w: dict, tokens, dtype=torch.float64):
     """-> (logits [T, vocab], residual stream after every layer run [runs, T, W])."""
     s = Stepper(cfg, w, dtype)
