@@ -287,7 +287,7 @@ int launch_conv_unit_finish(const float* proj, int ld, const StateGeom& g, int t
                             const int32_t* row_first, const int32_t* row_end, const int32_t* positions, const int32_t* slots, float unit_eps,
                             float* out, float* beta_out, int T, cudaStream_t s) {
   if (T <= 0) return 0;
-  B2_REQUIRE(taps >= 1 && conv_w && ring && row_seq && row_first && row_end, "conv_unit_finish: the convolution needs its weights and state");
+  B2_REQUIRE(taps >= 1 && conv_w && (ring || taps == 1) && row_seq && row_first && row_end, "conv_unit_finish: the convolution needs its weights and state");
   const int C = 2 * g.kv_heads * g.dim + g.heads * g.vdim;
   B2_CUDA_OK(b2_launch(conv_unit_finish_kernel, dim3(T), dim3(128), 0, s, proj, ld, g, taps, conv_w, (const float*)ring, row_seq, row_first,
                        positions, slots, unit_eps, out, beta_out));
