@@ -128,7 +128,9 @@ constexpr int SC_LANES = 4;     // lanes that share a state column
 constexpr int SC_COLS = 64;     // columns of a CTA at most
 constexpr int SC_CHUNK = 16;    // tokens staged at a time
 
-// grid (portions, heads, column tiles); block cols * 4.  DPT = key channels per lane (dim <= 4 * DPT).
+// grid (portions, heads, column tiles); block cols * 4.  DPT = key channels per lane (dim <= 4 * DPT).  Shared-memory rows hold lane j's
+// channels side by side (channel i * 4 + j at j * (DPT + 4) + i; the pad of four words spreads the four lanes over the banks), so a
+// lane reads its channels of q, k and the decay sixteen bytes at a time.
 template <int DPT, int RULE>
 __global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
                                                                        const float* __restrict__ v, int ldv, const float* __restrict__ decay,
@@ -137,9 +139,11 @@ __global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const fl
                                                                        const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_first,
                                                                        const int32_t* __restrict__ row_end, const int32_t* __restrict__ positions,
                                                                        const int32_t* __restrict__ slots, float* __restrict__ out, int cols) {
-  constexpr int DP = DPT * SC_LANES;
+  constexpr int LS = DPT + 4;               // words of one lane's channels in a staged row
+  constexpr int RS = LS * SC_LANES;         // words of a staged row
   constexpr int CH = DPT >= 64 ? SC_CHUNK / 2 : SC_CHUNK;   // (static shared memory ends at 48 KB)
-  __shared__ __align__(16) float qs[CH][DP], ks[CH][DP], as[CH][DP];
+  constexpr int VW = DPT >= 4 ? 4 : 2;      // channels per shared-memory load
+  __shared__ __align__(16) float qs[CH][RS], ks[CH][RS], as[CH][RS];
   __shared__ float vs[CH][SC_COLS], bs[CH];
   pdl_wait();
   pdl_launch_dependents();
@@ -163,16 +167,17 @@ __global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const fl
     s[i] = (pos0 > 0 && live && d < g.dim) ? s_in[(size_t)d * g.vdim + col] : 0.f;
   }
   const int nthreads = blockDim.x;
+  constexpr int DP = DPT * SC_LANES;
   for (int c0 = 0; c0 < n; c0 += CH) {
     const int cn = min(CH, n - c0);
     __syncthreads();   // the chunk before this one has been consumed
     for (int i = threadIdx.x; i < cn * DP; i += nthreads) {
-      const int tt = i / DP, d = i % DP;
+      const int tt = i / DP, d = i % DP, at = (d % SC_LANES) * LS + d / SC_LANES;
       const size_t row = (size_t)(first + c0 + tt);
       const bool in = d < g.dim;
-      qs[tt][d] = in ? q[row * ldq + kh * g.dim + d] * qscale : 0.f;
-      ks[tt][d] = in ? k[row * ldk + kh * g.dim + d] : 0.f;
-      as[tt][d] = in ? decay[row * ((size_t)g.heads * g.dim) + a * g.dim + d] : 1.f;
+      qs[tt][at] = in ? q[row * ldq + kh * g.dim + d] * qscale : 0.f;
+      ks[tt][at] = in ? k[row * ldk + kh * g.dim + d] : 0.f;
+      as[tt][at] = in ? decay[row * ((size_t)g.heads * g.dim) + a * g.dim + d] : 1.f;
     }
     for (int i = threadIdx.x; i < cn * cols; i += nthreads) {
       const int tt = i / cols, c = i % cols;
@@ -183,30 +188,56 @@ __global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const fl
     __syncthreads();
     for (int tt = 0; tt < cn; ++tt) {
       const float vc = vs[tt][ci];
+      const float* ap = &as[tt][j * LS];
+      const float* kp = &ks[tt][j * LS];
+      const float* qp = &qs[tt][j * LS];
+      float av[VW], kw[VW], qv[VW];
+      auto load = [&](const float* p, int i, float* dst) {
+        if constexpr (VW == 4) {
+          const float4 x = *reinterpret_cast<const float4*>(p + i);
+          dst[0] = x.x; dst[1] = x.y; dst[2] = x.z; dst[3] = x.w;
+        } else {
+          const float2 x = *reinterpret_cast<const float2*>(p + i);
+          dst[0] = x.x; dst[1] = x.y;
+        }
+      };
       float acc = 0.f;
       if (RULE == STATE_RULE_DECAY) {
 #pragma unroll
-        for (int i = 0; i < DPT; ++i) {
-          const int d = i * SC_LANES + j;
-          s[i] = fmaf(as[tt][d], s[i], ks[tt][d] * vc);
-          acc = fmaf(s[i], qs[tt][d], acc);
+        for (int i = 0; i < DPT; i += VW) {
+          load(ap, i, av);
+          load(kp, i, kw);
+          load(qp, i, qv);
+#pragma unroll
+          for (int x = 0; x < VW; ++x) {
+            s[i + x] = fmaf(av[x], s[i + x], kw[x] * vc);
+            acc = fmaf(s[i + x], qv[x], acc);
+          }
         }
       } else {
         float kv = 0.f;
 #pragma unroll
-        for (int i = 0; i < DPT; ++i) {
-          const int d = i * SC_LANES + j;
-          s[i] *= as[tt][d];
-          kv = fmaf(s[i], ks[tt][d], kv);
+        for (int i = 0; i < DPT; i += VW) {
+          load(ap, i, av);
+          load(kp, i, kw);
+#pragma unroll
+          for (int x = 0; x < VW; ++x) {
+            s[i + x] *= av[x];
+            kv = fmaf(s[i + x], kw[x], kv);
+          }
         }
         kv += __shfl_xor_sync(0xffffffffu, kv, 1);
         kv += __shfl_xor_sync(0xffffffffu, kv, 2);
         const float u = bs[tt] * (vc - kv);
 #pragma unroll
-        for (int i = 0; i < DPT; ++i) {
-          const int d = i * SC_LANES + j;
-          s[i] = fmaf(ks[tt][d], u, s[i]);
-          acc = fmaf(s[i], qs[tt][d], acc);
+        for (int i = 0; i < DPT; i += VW) {
+          load(kp, i, kw);
+          load(qp, i, qv);
+#pragma unroll
+          for (int x = 0; x < VW; ++x) {
+            s[i + x] = fmaf(kw[x], u, s[i + x]);
+            acc = fmaf(s[i + x], qv[x], acc);
+          }
         }
       }
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
@@ -305,7 +336,9 @@ int launch_state_scan(const float* q, int ldq, const float* k, int ldk, const fl
   B2_REQUIRE(g.rule == STATE_RULE_DECAY || (g.rule == STATE_RULE_DELTA && beta != nullptr), "state_scan: rule %d", g.rule);
   int dpt = 2;
   while (dpt * SC_LANES < g.dim) dpt *= 2;
-  const int cols = std::min(SC_COLS, (g.vdim + 7) / 8 * 8);
+  // as many columns per CTA as still leave two CTAs for every SM (a column's arithmetic does not depend on the tile it falls into)
+  int cols = std::min(SC_COLS, (g.vdim + 7) / 8 * 8);
+  while (cols > 8 && (long)portions * g.heads * ((g.vdim + cols - 1) / cols) < 2L * device_num_sms()) cols = (cols / 2 + 7) / 8 * 8;
   const dim3 grid(portions, g.heads, (g.vdim + cols - 1) / cols), block(cols * SC_LANES);
   if (g.rule == STATE_RULE_DECAY)
     return launch_scan_rule<STATE_RULE_DECAY>(dpt, grid, block, s, q, ldq, k, ldk, v, ldv, decay, beta, g, qscale, state, last_rows, row_seq,

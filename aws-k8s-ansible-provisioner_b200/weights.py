@@ -151,3 +151,71 @@ def kedasun_random_state_dict(model_cfg: dict, seed: int = 0) -> dict[str, torch
             t = torch.randn(shape, generator=g) * (shape[-1] ** -0.5)
         sd[name] = t.to(torch.bfloat16)
     return sd
+
+
+def bumalix_tensor_shapes(model_cfg: dict, rank_a: int = 16, rank_g: int = 24) -> dict[str, tuple[int, ...]]:
+    """Tensor names and shapes of a Bumalix checkpoint for the dict its config.json holds.  The widths of the low-rank first stages
+    (a1, g1) are not in the config -- a checkpoint's tensors carry them -- so they are arguments here."""
+    W, V = model_cfg["width"], model_cfg["vocab"]
+    s: dict[str, tuple[int, ...]] = {"embed": (V, W)}
+    if model_cfg.get("loop"):
+        s["loop.in"] = (W, 2 * W)
+    for i, layer in enumerate(model_cfg["layers"]):
+        m, mlp, p = layer["mixer"], layer.get("mlp"), f"l{i}."
+        s[p + "norm1"] = (W,)
+        if layer["type"] == "parallel":
+            a, b, q = m["left"], m["right"], p + "mix.left."
+            H, G, D, Dv = a["heads"], a.get("kv_heads", a["heads"]), a["dim"], a["vdim"]
+            for n, c in (("q", H * D), ("k", G * D), ("v", G * Dv)):
+                s[q + n], s[q + n + ".b"] = (c, W), (c,)
+            s[q + "q.norm"], s[q + "k.norm"], s[q + "o"], s[q + "out"] = (H * D,), (G * D,), (W, H * Dv), (W,)
+            H, D, Dv, q = b["heads"], b["dim"], b["vdim"], p + "mix.right."
+            s[q + "q"], s[q + "k"], s[q + "v"], s[q + "g"], s[q + "o"] = (H * D, W), (H * D, W), (H * Dv, W), (H * Dv, W), (W, H * Dv)
+            s[q + "norm"], s[q + "a1"], s[q + "a2"], s[q + "a2.b"], s[q + "out"] = (Dv,), (rank_a, W), (H * D, rank_a), (H * D,), (W,)
+        else:
+            H, G, D, Dv, q = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m["vdim"], p + "mix."
+            for n, c in (("q", G * D), ("k", G * D), ("v", H * Dv)):
+                s[q + n], s[q + n + ".conv"] = (c, W), (c, m["conv"])
+            s[q + "b"], s[q + "A_log"], s[q + "norm"], s[q + "o"] = (H, W), (H,), (Dv,), (W, H * Dv)
+            s[q + "a1"], s[q + "a2"], s[q + "dt_bias"], s[q + "g1"], s[q + "g2"] = (rank_a, W), (H * D, rank_a), (H * D,), (rank_g, W), (H * Dv, rank_g)
+        if mlp is not None and mlp["kind"] == "dense":
+            s[p + "mlp.up"], s[p + "mlp.down"], s[p + "mlp.act"] = (mlp["ff"], W), (W, mlp["ff"]), (4,)
+        elif mlp is not None:
+            F = mlp["expert"]["ff"]
+            s[p + "mlp.router"] = (mlp["router"]["experts"], W)
+            for e in range(mlp["router"]["experts"]):
+                s[p + f"mlp.e{e}.gate"], s[p + f"mlp.e{e}.up"], s[p + f"mlp.e{e}.down"] = (F, W), (F, W), (W, F)
+            if mlp.get("shared"):
+                Fs = mlp["shared"]["ff"]
+                s[p + "mlp.shared.gate"], s[p + "mlp.shared.up"], s[p + "mlp.shared.down"] = (Fs, W), (Fs, W), (W, Fs)
+    s["final.norm"] = (W,)
+    s["head"] = (V, W)
+    return s
+
+
+def bumalix_random_state_dict(model_cfg: dict, seed: int = 0, rank_a: int = 16, rank_g: int = 24) -> dict[str, torch.Tensor]:
+    """Random bf16 weights scaled by 1/sqrt(fan-in), gains around one, decays that forget over tens to hundreds of tokens."""
+    g = torch.Generator().manual_seed(seed)
+    sd = {}
+    for name, shape in bumalix_tensor_shapes(model_cfg, rank_a, rank_g).items():
+        last = name.rsplit(".", 1)[-1]
+        if "norm" in name or last == "out":
+            t = 1.0 + 0.1 * torch.randn(shape, generator=g)
+        elif last == "act":
+            t = torch.tensor([0.6, 0.3, 0.2, 0.0])
+        elif last == "A_log":
+            t = torch.log(0.5 + 2.0 * torch.rand(shape, generator=g))
+        elif last == "dt_bias":
+            t = torch.randn(shape, generator=g) - 3.0
+        elif name.endswith("a2.b"):
+            t = torch.randn(shape, generator=g) + 3.0
+        elif last == "b" and len(shape) == 1:
+            t = 0.1 * torch.randn(shape, generator=g)
+        elif last == "conv":
+            t = 0.5 * torch.randn(shape, generator=g)
+        elif name == "embed":
+            t = 0.5 * torch.randn(shape, generator=g)
+        else:
+            t = torch.randn(shape, generator=g) * (shape[-1] ** -0.5)
+        sd[name] = t.to(torch.bfloat16)
+    return sd

@@ -461,8 +461,31 @@ def kedasun_model_cfg(width, heads, kv, ff, layers=4, vocab=32000):
     return {"architecture": "Kedasun", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6, "groups": 4}, "layers": ls}
 
 
+# ---- --family bumalix: width, heads (128 wide, two per kv head), Qwen3's feed-forward width.  Four layers: windowed softmax attention beside gated
+#      linear attention twice, the gated delta rule twice; a polynomial feed-forward and routed gated experts (16, two chosen, one shared) with
+#      Qwen3's active parameter count; one pass of the loop over the two middle layers; vocab 32000
+BUMALIX_SIZES = {"w1024": (1024, 8, 3072), "w2048": (2048, 16, 6144), "w4096": (4096, 32, 11008)}
+
+
+def bumalix_model_cfg(width, heads, inter, layers=4, vocab=32000):
+    par = {"left": {"heads": heads, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 512}},
+           "right": {"heads": heads // 2, "dim": 128, "vdim": 256, "tau": 16.0}}
+    dlt = {"heads": heads, "kv_heads": heads, "dim": 128, "vdim": 128, "conv": 4}
+    dense = {"kind": "dense", "ff": (3 * inter // 2 + 255) // 256 * 256}
+    moe = {"kind": "moe", "expert": {"ff": (inter // 3 + 63) // 64 * 64}, "router": {"experts": 16, "top": 2}, "shared": {"ff": (inter // 3 + 63) // 64 * 64}}
+    ls = [{"type": "channel_delta" if i % 2 else "parallel", "mixer": dlt if i % 2 else par, "mlp": moe if i % 4 in (1, 2) else dense} for i in range(layers)]
+    return {"architecture": "Bumalix", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "loop": {"start": 1, "stop": 3, "times": 1}, "layers": ls}
+
+
 def family_models(pkg, weights, family, tag):
     """(name, engine configuration, state-dict maker) of the family's model and of Qwen3 at the same width, depth, heads and feed-forward size."""
+    if family == "bumalix":
+        width, heads, inter = BUMALIX_SIZES[tag]
+        mc = bumalix_model_cfg(width, heads, inter)
+        return [("bumalix", pkg.EngineConfig.bumalix(mc), lambda c: weights.bumalix_random_state_dict(mc, seed=0)),
+                ("qwen3", pkg.EngineConfig(num_layers=4, hidden=width, num_q_heads=heads, num_kv_heads=heads // 2, head_dim=128, intermediate=inter, vocab=32000),
+                 lambda c: weights.random_state_dict(c, seed=0))]
     if family == "kedasun":
         width, heads, kv, ff = KEDASUN_SIZES[tag]
         mc = kedasun_model_cfg(width, heads, kv, ff)
@@ -478,7 +501,7 @@ def family_models(pkg, weights, family, tag):
 
 
 def run_family(args, local):
-    """Prefill and decode throughput of a layer-list family (Lerasun, Kedasun) at layer sizes of real models (random weights), and of
+    """Prefill and decode throughput of a layer-list family (Lerasun, Kedasun, Bumalix) at layer sizes of real models (random weights), and of
     Qwen3 at the same width, depth, head count and (active) feed-forward size: one JSON line per size and model, with the decode step's
     per-kernel-class times (CUDA events around every launch of an eager step)."""
     import torch
@@ -533,7 +556,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--value-only", action="store_true", help="device-resident timing only (ablation runs)")
-    ap.add_argument("--family", default="", choices=["", "lerasun", "kedasun"],
+    ap.add_argument("--family", default="", choices=["", "lerasun", "kedasun", "bumalix"],
                     help="instead of the headline workload: the named family beside the closest GQA model at equal size (one GPU)")
     ap.add_argument("--family-sizes", default="w1024,w2048,w4096")
     ap.add_argument("--family-only", default="", help="time only the named model of the pair (the family's name, or qwen3)")
