@@ -22,7 +22,7 @@
 // The scan is sequential in time and parallel over (sequence, head, value column): a CTA owns up to 64 columns of one
 // head's state for one portion, four lanes share a column and split the key channels (channel i * 4 + j belongs to
 // lane j, so the four lanes read consecutive shared-memory words), each lane keeps its channels of the column in
-// registers for the whole portion.  Tokens are staged through shared memory a chunk at a time.  The arithmetic of a token does
+// registers for the whole portion.  Tokens are staged through shared memory by asynchronous copies, a chunk ahead.  The arithmetic of a token does
 // not depend on where the portion was cut, so prefill, chunked prefill and token-by-token decoding give the same bits.
 //
 // Kernels:
@@ -41,26 +41,49 @@ __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
-// one warp per output channel group: lr [T][ld] fp32 (rank numbers per token at column lr_off)
+// A CTA takes LR_TOKENS tokens and 256 output channels; a thread owns one channel, reads its row of w2 once (sixteen numbers at a
+// time) and applies it to every token of the tile.  lr [T][ld] fp32 (rank numbers per token at column lr_off), staged in shared memory.
+constexpr int LR_TOKENS = 8;
 __global__ void __launch_bounds__(256) lowrank_act_kernel(const float* __restrict__ lr, int ld, int lr_off, int rank, const float* __restrict__ w2,
                                                           const float* __restrict__ bias, const float* __restrict__ rate_log, float rate,
-                                                          int per_head, int mode, float* __restrict__ out, int C) {
-  extern __shared__ float lrs[];
+                                                          int per_head, int mode, float* __restrict__ out, int C, int T) {
+  extern __shared__ float lrs[];   // [LR_TOKENS][rank]
   pdl_wait();
   pdl_launch_dependents();
-  const int t = blockIdx.x;
-  for (int i = threadIdx.x; i < rank; i += 256) lrs[i] = lr[(size_t)t * ld + lr_off + i];
+  const int t0 = blockIdx.x * LR_TOKENS, tn = min(LR_TOKENS, T - t0);
+  for (int i = threadIdx.x; i < tn * rank; i += 256) lrs[i] = lr[(size_t)(t0 + i / rank) * ld + lr_off + i % rank];
   __syncthreads();
-  for (int c = blockIdx.y * 256 + threadIdx.x; c < C; c += 256 * gridDim.y) {
-    const float* wr = w2 + (size_t)c * rank;
-    float z = 0.f;
-    for (int r = 0; r < rank; ++r) z = fmaf(wr[r], lrs[r], z);
-    if (bias) z += bias[c];
+  const int c = blockIdx.y * 256 + threadIdx.x;
+  if (c >= C) return;
+  const float* wr = w2 + (size_t)c * rank;
+  float z[LR_TOKENS];
+#pragma unroll
+  for (int tt = 0; tt < LR_TOKENS; ++tt) z[tt] = 0.f;
+  for (int r0 = 0; r0 < rank; r0 += 16) {
+    float w[16];
+#pragma unroll
+    for (int x = 0; x < 16; ++x) w[x] = r0 + x < rank ? wr[r0 + x] : 0.f;
+#pragma unroll
+    for (int tt = 0; tt < LR_TOKENS; ++tt) {
+      if (tt < tn) {
+        const float* l = lrs + tt * rank + r0;
+#pragma unroll
+        for (int x = 0; x < 16; ++x)
+          if (r0 + x < rank) z[tt] = fmaf(w[x], l[x], z[tt]);
+      }
+    }
+  }
+  const float b = bias ? bias[c] : 0.f;
+  const float rt = mode == LOWRANK_DECAY_SOFTPLUS ? expf(rate_log[c / per_head]) : rate;
+#pragma unroll
+  for (int tt = 0; tt < LR_TOKENS; ++tt) {
+    if (tt >= tn) break;
+    const float zz = z[tt] + b;
     float y;
-    if (mode == LOWRANK_SIGMOID) y = sigmoid_f(z);
-    else if (mode == LOWRANK_DECAY_SIGMOID_POW) y = expf(-rate * softplus_f(-z));              // sigmoid(z)^rate
-    else y = expf(-expf(rate_log[c / per_head]) * softplus_f(z));                              // exp(-exp(A) softplus(z))
-    out[(size_t)t * C + c] = y;
+    if (mode == LOWRANK_SIGMOID) y = sigmoid_f(zz);
+    else if (mode == LOWRANK_DECAY_SIGMOID_POW) y = expf(-rt * softplus_f(-zz));               // sigmoid(z)^rate
+    else y = expf(-rt * softplus_f(zz));                                                       // exp(-exp(A) softplus(z))
+    out[(size_t)(t0 + tt) * C + c] = y;
   }
 }
 
@@ -126,11 +149,19 @@ __global__ void __launch_bounds__(128) conv_ring_store_kernel(const float* __res
 
 constexpr int SC_LANES = 4;     // lanes that share a state column
 constexpr int SC_COLS = 64;     // columns of a CTA at most
-constexpr int SC_CHUNK = 16;    // tokens staged at a time
+constexpr int SC_CHUNK = 8;     // tokens of one stage (two stages)
+
+__device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // grid (portions, heads, column tiles); block cols * 4.  DPT = key channels per lane (dim <= 4 * DPT).  Shared-memory rows hold lane j's
 // channels side by side (channel i * 4 + j at j * (DPT + 4) + i; the pad of four words spreads the four lanes over the banks), so a
-// lane reads its channels of q, k and the decay sixteen bytes at a time.
+// lane reads its channels of q, k and the decay sixteen bytes at a time.  Tokens arrive by asynchronous copies, the chunk after the
+// one being worked on always in flight.  q is scaled at the read-out (S^T (c q) = c S^T q).
 template <int DPT, int RULE>
 __global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
                                                                        const float* __restrict__ v, int ldv, const float* __restrict__ decay,
@@ -143,8 +174,9 @@ __global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const fl
   constexpr int RS = LS * SC_LANES;         // words of a staged row
   constexpr int CH = DPT >= 64 ? SC_CHUNK / 2 : SC_CHUNK;   // (static shared memory ends at 48 KB)
   constexpr int VW = DPT >= 4 ? 4 : 2;      // channels per shared-memory load
-  __shared__ __align__(16) float qs[CH][RS], ks[CH][RS], as[CH][RS];
-  __shared__ float vs[CH][SC_COLS], bs[CH];
+  constexpr int DP = DPT * SC_LANES;
+  __shared__ __align__(16) float qs[2][CH][RS], ks[2][CH][RS], as[2][CH][RS];
+  __shared__ float vs[2][CH][SC_COLS], bs[2][CH];
   pdl_wait();
   pdl_launch_dependents();
   const int r_last = last_rows ? last_rows[blockIdx.x] : (int)blockIdx.x;
@@ -156,52 +188,73 @@ __global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const fl
   const int col = col0 + ci;
   const bool live = col < g.vdim;
   const int pos0 = positions[first], n = end - first;
+  const int nthreads = blockDim.x;
   const size_t head_floats = (size_t)g.dim * g.vdim;
   float* sbase = state + ((size_t)row_seq[first] * 2 * g.heads) * head_floats;
   const float* s_in = sbase + ((size_t)((pos0 + 1) & 1) * g.heads + a) * head_floats;
   float* s_out = sbase + ((size_t)((pos0 + n - 1) & 1) * g.heads + a) * head_floats;
+  // channels past dim and columns past vdim never change: zero keys, queries and values, a decay of one
+  for (int i = threadIdx.x; i < 2 * CH * (DP - g.dim); i += nthreads) {
+    const int st = i / (CH * (DP - g.dim)), rem = i % (CH * (DP - g.dim)), tt = rem / (DP - g.dim), d = g.dim + rem % (DP - g.dim);
+    const int at = (d % SC_LANES) * LS + d / SC_LANES;
+    qs[st][tt][at] = 0.f;
+    ks[st][tt][at] = 0.f;
+    as[st][tt][at] = 1.f;
+  }
+  const int vcols = min(cols, g.vdim - col0);
+  for (int i = threadIdx.x; i < 2 * CH * SC_COLS; i += nthreads) (&vs[0][0][0])[i] = 0.f;
+  __syncthreads();
+  auto issue = [&](int c0, int st) {
+    const int cn = min(CH, n - c0);
+    for (int i = threadIdx.x; i < cn * g.dim; i += nthreads) {
+      const int tt = i / g.dim, d = i % g.dim, at = (d % SC_LANES) * LS + d / SC_LANES;
+      const size_t row = (size_t)(first + c0 + tt);
+      cp_async_f32(&qs[st][tt][at], q + row * ldq + kh * g.dim + d);
+      cp_async_f32(&ks[st][tt][at], k + row * ldk + kh * g.dim + d);
+      cp_async_f32(&as[st][tt][at], decay + row * ((size_t)g.heads * g.dim) + a * g.dim + d);
+    }
+    for (int i = threadIdx.x; i < cn * vcols; i += nthreads) {
+      const int tt = i / vcols, c = i % vcols;
+      cp_async_f32(&vs[st][tt][c], v + (size_t)(first + c0 + tt) * ldv + a * g.vdim + col0 + c);
+    }
+    if (RULE == STATE_RULE_DELTA)
+      for (int i = threadIdx.x; i < cn; i += nthreads) cp_async_f32(&bs[st][i], beta + (size_t)(first + c0 + i) * g.heads + a);
+    cp_async_commit();
+  };
+  issue(0, 0);
   float s[DPT];
 #pragma unroll
   for (int i = 0; i < DPT; ++i) {
     const int d = i * SC_LANES + j;
     s[i] = (pos0 > 0 && live && d < g.dim) ? s_in[(size_t)d * g.vdim + col] : 0.f;
   }
-  const int nthreads = blockDim.x;
-  constexpr int DP = DPT * SC_LANES;
-  for (int c0 = 0; c0 < n; c0 += CH) {
+  auto load = [&](const float* p, int i, float* dst) {
+    if constexpr (VW == 4) {
+      const float4 x = *reinterpret_cast<const float4*>(p + i);
+      dst[0] = x.x; dst[1] = x.y; dst[2] = x.z; dst[3] = x.w;
+    } else {
+      const float2 x = *reinterpret_cast<const float2*>(p + i);
+      dst[0] = x.x; dst[1] = x.y;
+    }
+  };
+  int st = 0;
+  for (int c0 = 0; c0 < n; c0 += CH, st ^= 1) {
     const int cn = min(CH, n - c0);
-    __syncthreads();   // the chunk before this one has been consumed
-    for (int i = threadIdx.x; i < cn * DP; i += nthreads) {
-      const int tt = i / DP, d = i % DP, at = (d % SC_LANES) * LS + d / SC_LANES;
-      const size_t row = (size_t)(first + c0 + tt);
-      const bool in = d < g.dim;
-      qs[tt][at] = in ? q[row * ldq + kh * g.dim + d] * qscale : 0.f;
-      ks[tt][at] = in ? k[row * ldk + kh * g.dim + d] : 0.f;
-      as[tt][at] = in ? decay[row * ((size_t)g.heads * g.dim) + a * g.dim + d] : 1.f;
+    if (c0 + CH < n) {
+      issue(c0 + CH, st ^ 1);     // (every thread left that stage at the barrier that ended the chunk before this one)
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
-    for (int i = threadIdx.x; i < cn * cols; i += nthreads) {
-      const int tt = i / cols, c = i % cols;
-      vs[tt][c] = col0 + c < g.vdim ? v[(size_t)(first + c0 + tt) * ldv + a * g.vdim + col0 + c] : 0.f;
-    }
-    if (RULE == STATE_RULE_DELTA)
-      for (int i = threadIdx.x; i < cn; i += nthreads) bs[i] = beta[(size_t)(first + c0 + i) * g.heads + a];
     __syncthreads();
     for (int tt = 0; tt < cn; ++tt) {
-      const float vc = vs[tt][ci];
-      const float* ap = &as[tt][j * LS];
-      const float* kp = &ks[tt][j * LS];
-      const float* qp = &qs[tt][j * LS];
-      float av[VW], kw[VW], qv[VW];
-      auto load = [&](const float* p, int i, float* dst) {
-        if constexpr (VW == 4) {
-          const float4 x = *reinterpret_cast<const float4*>(p + i);
-          dst[0] = x.x; dst[1] = x.y; dst[2] = x.z; dst[3] = x.w;
-        } else {
-          const float2 x = *reinterpret_cast<const float2*>(p + i);
-          dst[0] = x.x; dst[1] = x.y;
-        }
-      };
-      float acc = 0.f;
+      const float vc = vs[st][tt][ci];
+      const float* ap = &as[st][tt][j * LS];
+      const float* kp = &ks[st][tt][j * LS];
+      const float* qp = &qs[st][tt][j * LS];
+      float av[VW], kw[VW], qv[VW], acc[VW];
+#pragma unroll
+      for (int x = 0; x < VW; ++x) acc[x] = 0.f;
       if (RULE == STATE_RULE_DECAY) {
 #pragma unroll
         for (int i = 0; i < DPT; i += VW) {
@@ -211,11 +264,13 @@ __global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const fl
 #pragma unroll
           for (int x = 0; x < VW; ++x) {
             s[i + x] = fmaf(av[x], s[i + x], kw[x] * vc);
-            acc = fmaf(s[i + x], qv[x], acc);
+            acc[x] = fmaf(s[i + x], qv[x], acc[x]);
           }
         }
       } else {
-        float kv = 0.f;
+        float kv[VW];
+#pragma unroll
+        for (int x = 0; x < VW; ++x) kv[x] = 0.f;
 #pragma unroll
         for (int i = 0; i < DPT; i += VW) {
           load(ap, i, av);
@@ -223,12 +278,13 @@ __global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const fl
 #pragma unroll
           for (int x = 0; x < VW; ++x) {
             s[i + x] *= av[x];
-            kv = fmaf(s[i + x], kw[x], kv);
+            kv[x] = fmaf(s[i + x], kw[x], kv[x]);
           }
         }
-        kv += __shfl_xor_sync(0xffffffffu, kv, 1);
-        kv += __shfl_xor_sync(0xffffffffu, kv, 2);
-        const float u = bs[tt] * (vc - kv);
+        float kvs = VW == 4 ? (kv[0] + kv[1]) + (kv[2] + kv[VW - 1]) : kv[0] + kv[1];
+        kvs += __shfl_xor_sync(0xffffffffu, kvs, 1);
+        kvs += __shfl_xor_sync(0xffffffffu, kvs, 2);
+        const float u = bs[st][tt] * (vc - kvs);
 #pragma unroll
         for (int i = 0; i < DPT; i += VW) {
           load(kp, i, kw);
@@ -236,14 +292,16 @@ __global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const fl
 #pragma unroll
           for (int x = 0; x < VW; ++x) {
             s[i + x] = fmaf(kw[x], u, s[i + x]);
-            acc = fmaf(s[i + x], qv[x], acc);
+            acc[x] = fmaf(s[i + x], qv[x], acc[x]);
           }
         }
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      if (j == 0 && live) out[(size_t)(first + c0 + tt) * ((size_t)g.heads * g.vdim) + a * g.vdim + col] = acc;
+      float o = VW == 4 ? (acc[0] + acc[1]) + (acc[2] + acc[VW - 1]) : acc[0] + acc[1];
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (j == 0 && live) out[(size_t)(first + c0 + tt) * ((size_t)g.heads * g.vdim) + a * g.vdim + col] = o * qscale;
     }
+    __syncthreads();   // the chunk has been consumed: its stage may be filled again
   }
   if (live) {
 #pragma unroll
@@ -306,11 +364,11 @@ int launch_scan_rule(int dpt, dim3 grid, dim3 block, cudaStream_t s, const float
 int launch_lowrank_act(const float* lr, int ld, int lr_off, int rank, const float* w2, const float* bias, int mode, float rate,
                        const float* rate_log, int per_head, float* out, int T, int C, cudaStream_t s) {
   if (T <= 0 || C <= 0) return 0;
-  B2_REQUIRE(rank >= 1 && rank <= 8192, "lowrank_act: rank %d", rank);
+  B2_REQUIRE(rank >= 1 && rank <= 1024, "lowrank_act: rank %d (at most 1024)", rank);
   B2_REQUIRE(mode != LOWRANK_DECAY_SOFTPLUS || (rate_log != nullptr && per_head >= 1), "lowrank_act: the softplus decay needs a rate per head");
-  const dim3 grid(T, T >= 512 ? 1 : std::max(1, std::min((C + 255) / 256, 512 / T)));
-  B2_CUDA_OK(b2_launch(lowrank_act_kernel, grid, dim3(256), (size_t)rank * 4, s, lr, ld, lr_off, rank, w2, bias, rate_log, rate,
-                       per_head > 0 ? per_head : 1, mode, out, C));
+  const dim3 grid((T + LR_TOKENS - 1) / LR_TOKENS, (C + 255) / 256);
+  B2_CUDA_OK(b2_launch(lowrank_act_kernel, grid, dim3(256), (size_t)LR_TOKENS * rank * 4, s, lr, ld, lr_off, rank, w2, bias, rate_log, rate,
+                       per_head > 0 ? per_head : 1, mode, out, C, T));
   return 0;
 }
 
@@ -338,7 +396,7 @@ int launch_state_scan(const float* q, int ldq, const float* k, int ldk, const fl
   while (dpt * SC_LANES < g.dim) dpt *= 2;
   // as many columns per CTA as still leave two CTAs for every SM (a column's arithmetic does not depend on the tile it falls into)
   int cols = std::min(SC_COLS, (g.vdim + 7) / 8 * 8);
-  while (cols > 8 && (long)portions * g.heads * ((g.vdim + cols - 1) / cols) < 2L * device_num_sms()) cols = (cols / 2 + 7) / 8 * 8;
+  while (cols > 16 && (long)portions * g.heads * ((g.vdim + cols - 1) / cols) < 2L * device_num_sms()) cols = (cols / 2 + 7) / 8 * 8;
   const dim3 grid(portions, g.heads, (g.vdim + cols - 1) / cols), block(cols * SC_LANES);
   if (g.rule == STATE_RULE_DECAY)
     return launch_scan_rule<STATE_RULE_DECAY>(dpt, grid, block, s, q, ldq, k, ldk, v, ldv, decay, beta, g, qscale, state, last_rows, row_seq,
