@@ -19,10 +19,9 @@
 // reads.  The convolution keeps its last inputs in a ring of `taps` rows per slot indexed by position mod taps, for the
 // same reason.
 //
-// The scan is sequential in time and parallel over (sequence, head, value column): a CTA owns up to 64 columns of one
-// head's state for one portion, four lanes share a column and split the key channels (channel i * 4 + j belongs to
-// lane j, so the four lanes read consecutive shared-memory words), each lane keeps its channels of the column in
-// registers for the whole portion.  Tokens are staged through shared memory by asynchronous copies, a chunk ahead.  The arithmetic of a token does
+// The scan is sequential in time and parallel over (sequence, head, value column): a CTA owns up to 128 columns of one
+// head's state for one portion, eight lanes share four neighbouring columns and split the key channels (channel i * 8 + j
+// belongs to lane j), each lane keeps its channels of its columns in registers for the whole portion.  Tokens are staged through shared memory by asynchronous copies, a chunk ahead.  The arithmetic of a token does
 // not depend on where the portion was cut, so prefill, chunked prefill and token-by-token decoding give the same bits.
 //
 // Kernels:
@@ -147,8 +146,7 @@ __global__ void __launch_bounds__(128) conv_ring_store_kernel(const float* __res
   for (int c = threadIdx.x; c < C; c += 128) dst[c] = row[c];
 }
 
-constexpr int SC_LANES = 4;     // lanes that share a state column
-constexpr int SC_COLS = 64;     // columns of a CTA at most
+constexpr int SC_LANES = 8;     // lanes that share a group of state columns and split the key channels
 constexpr int SC_CHUNK = 8;     // tokens of one stage (two stages)
 
 __device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* gsrc) {
@@ -158,25 +156,28 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// grid (portions, heads, column tiles); block cols * 4.  DPT = key channels per lane (dim <= 4 * DPT).  Shared-memory rows hold lane j's
-// channels side by side (channel i * 4 + j at j * (DPT + 4) + i; the pad of four words spreads the four lanes over the banks), so a
-// lane reads its channels of q, k and the decay sixteen bytes at a time.  Tokens arrive by asynchronous copies, the chunk after the
-// one being worked on always in flight.  q is scaled at the read-out (S^T (c q) = c S^T q).
-template <int DPT, int RULE>
-__global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
-                                                                       const float* __restrict__ v, int ldv, const float* __restrict__ decay,
-                                                                       const float* __restrict__ beta, StateGeom g, float qscale,
-                                                                       float* __restrict__ state, const int32_t* __restrict__ last_rows,
-                                                                       const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_first,
-                                                                       const int32_t* __restrict__ row_end, const int32_t* __restrict__ positions,
-                                                                       const int32_t* __restrict__ slots, float* __restrict__ out, int cols) {
+// grid (portions, heads, column tiles); block (cols / NC) * 8.  Eight lanes share NC neighbouring columns of the state and split the key
+// channels (channel i * 8 + j belongs to lane j; DPT channels per lane, dim <= 8 * DPT), so a value of q, k or the decay read from shared
+// memory serves NC columns.  Shared-memory rows hold lane j's channels side by side (at j * (DPT + 4) + i; the pad of four words spreads the
+// eight lanes over the banks) and are read sixteen bytes at a time.  Tokens arrive by asynchronous copies, the chunk after the one being
+// worked on always in flight.  q is scaled at the read-out (S^T (c q) = c S^T q).
+template <int DPT, int NC, int RULE>
+__global__ void __launch_bounds__(256) state_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
+                                                         const float* __restrict__ v, int ldv, const float* __restrict__ decay,
+                                                         const float* __restrict__ beta, StateGeom g, float qscale, float* __restrict__ state,
+                                                         const int32_t* __restrict__ last_rows, const int32_t* __restrict__ row_seq,
+                                                         const int32_t* __restrict__ row_first, const int32_t* __restrict__ row_end,
+                                                         const int32_t* __restrict__ positions, const int32_t* __restrict__ slots,
+                                                         float* __restrict__ out, int cols) {
   constexpr int LS = DPT + 4;               // words of one lane's channels in a staged row
   constexpr int RS = LS * SC_LANES;         // words of a staged row
-  constexpr int CH = DPT >= 64 ? SC_CHUNK / 2 : SC_CHUNK;   // (static shared memory ends at 48 KB)
-  constexpr int VW = DPT >= 4 ? 4 : 2;      // channels per shared-memory load
+  constexpr int CH = DPT >= 32 ? SC_CHUNK / 2 : SC_CHUNK;   // (static shared memory ends at 48 KB)
+  constexpr int VW = DPT >= 4 ? 4 : DPT;    // channels per shared-memory load
   constexpr int DP = DPT * SC_LANES;
+  constexpr int MAXC = 32 * NC;             // columns of a CTA at most
   __shared__ __align__(16) float qs[2][CH][RS], ks[2][CH][RS], as[2][CH][RS];
-  __shared__ float vs[2][CH][SC_COLS], bs[2][CH];
+  __shared__ __align__(16) float vs[2][CH][MAXC];
+  __shared__ float bs[2][CH];
   pdl_wait();
   pdl_launch_dependents();
   const int r_last = last_rows ? last_rows[blockIdx.x] : (int)blockIdx.x;
@@ -184,9 +185,8 @@ __global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const fl
   if (slots[first] < 0) return;   // padding row of a decode bucket
   const int a = blockIdx.y, kh = a / (g.heads / g.kv_heads);
   const int col0 = blockIdx.z * cols;
-  const int ci = threadIdx.x / SC_LANES, j = threadIdx.x % SC_LANES;
-  const int col = col0 + ci;
-  const bool live = col < g.vdim;
+  const int grp = threadIdx.x / SC_LANES, j = threadIdx.x % SC_LANES;
+  const int cl = grp * NC;                  // first of this thread's columns within the CTA's tile
   const int pos0 = positions[first], n = end - first;
   const int nthreads = blockDim.x;
   const size_t head_floats = (size_t)g.dim * g.vdim;
@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const fl
     as[st][tt][at] = 1.f;
   }
   const int vcols = min(cols, g.vdim - col0);
-  for (int i = threadIdx.x; i < 2 * CH * SC_COLS; i += nthreads) (&vs[0][0][0])[i] = 0.f;
+  for (int i = threadIdx.x; i < 2 * CH * MAXC; i += nthreads) (&vs[0][0][0])[i] = 0.f;
   __syncthreads();
   auto issue = [&](int c0, int st) {
     const int cn = min(CH, n - c0);
@@ -222,19 +222,22 @@ __global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const fl
     cp_async_commit();
   };
   issue(0, 0);
-  float s[DPT];
+  float s[DPT][NC];
 #pragma unroll
   for (int i = 0; i < DPT; ++i) {
     const int d = i * SC_LANES + j;
-    s[i] = (pos0 > 0 && live && d < g.dim) ? s_in[(size_t)d * g.vdim + col] : 0.f;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) s[i][c] = (pos0 > 0 && d < g.dim && col0 + cl + c < g.vdim) ? s_in[(size_t)d * g.vdim + col0 + cl + c] : 0.f;
   }
   auto load = [&](const float* p, int i, float* dst) {
     if constexpr (VW == 4) {
       const float4 x = *reinterpret_cast<const float4*>(p + i);
       dst[0] = x.x; dst[1] = x.y; dst[2] = x.z; dst[3] = x.w;
-    } else {
+    } else if constexpr (VW == 2) {
       const float2 x = *reinterpret_cast<const float2*>(p + i);
       dst[0] = x.x; dst[1] = x.y;
+    } else {
+      dst[0] = p[i];
     }
   };
   int st = 0;
@@ -248,13 +251,20 @@ __global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const fl
     }
     __syncthreads();
     for (int tt = 0; tt < cn; ++tt) {
-      const float vc = vs[st][tt][ci];
+      float vc[NC];
+      if constexpr (NC == 4) {
+        const float4 x = *reinterpret_cast<const float4*>(&vs[st][tt][cl]);
+        vc[0] = x.x; vc[1] = x.y; vc[2] = x.z; vc[3] = x.w;
+      } else {
+#pragma unroll
+        for (int c = 0; c < NC; ++c) vc[c] = vs[st][tt][cl + c];
+      }
       const float* ap = &as[st][tt][j * LS];
       const float* kp = &ks[st][tt][j * LS];
       const float* qp = &qs[st][tt][j * LS];
-      float av[VW], kw[VW], qv[VW], acc[VW];
+      float av[VW], kw[VW], qv[VW], acc[NC];
 #pragma unroll
-      for (int x = 0; x < VW; ++x) acc[x] = 0.f;
+      for (int c = 0; c < NC; ++c) acc[c] = 0.f;
       if (RULE == STATE_RULE_DECAY) {
 #pragma unroll
         for (int i = 0; i < DPT; i += VW) {
@@ -262,53 +272,71 @@ __global__ void __launch_bounds__(SC_COLS * SC_LANES) state_scan_kernel(const fl
           load(kp, i, kw);
           load(qp, i, qv);
 #pragma unroll
-          for (int x = 0; x < VW; ++x) {
-            s[i + x] = fmaf(av[x], s[i + x], kw[x] * vc);
-            acc[x] = fmaf(s[i + x], qv[x], acc[x]);
-          }
+          for (int x = 0; x < VW; ++x)
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+              s[i + x][c] = fmaf(av[x], s[i + x][c], kw[x] * vc[c]);
+              acc[c] = fmaf(s[i + x][c], qv[x], acc[c]);
+            }
         }
       } else {
-        float kv[VW];
+        float kv[NC];
 #pragma unroll
-        for (int x = 0; x < VW; ++x) kv[x] = 0.f;
+        for (int c = 0; c < NC; ++c) kv[c] = 0.f;
 #pragma unroll
         for (int i = 0; i < DPT; i += VW) {
           load(ap, i, av);
           load(kp, i, kw);
 #pragma unroll
-          for (int x = 0; x < VW; ++x) {
-            s[i + x] *= av[x];
-            kv[x] = fmaf(s[i + x], kw[x], kv[x]);
-          }
+          for (int x = 0; x < VW; ++x)
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+              s[i + x][c] *= av[x];
+              kv[c] = fmaf(s[i + x][c], kw[x], kv[c]);
+            }
         }
-        float kvs = VW == 4 ? (kv[0] + kv[1]) + (kv[2] + kv[VW - 1]) : kv[0] + kv[1];
-        kvs += __shfl_xor_sync(0xffffffffu, kvs, 1);
-        kvs += __shfl_xor_sync(0xffffffffu, kvs, 2);
-        const float u = bs[st][tt] * (vc - kvs);
+        const float bt = bs[st][tt];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+          kv[c] += __shfl_xor_sync(0xffffffffu, kv[c], 1);
+          kv[c] += __shfl_xor_sync(0xffffffffu, kv[c], 2);
+          kv[c] += __shfl_xor_sync(0xffffffffu, kv[c], 4);
+          kv[c] = bt * (vc[c] - kv[c]);     // u
+        }
 #pragma unroll
         for (int i = 0; i < DPT; i += VW) {
           load(kp, i, kw);
           load(qp, i, qv);
 #pragma unroll
-          for (int x = 0; x < VW; ++x) {
-            s[i + x] = fmaf(kw[x], u, s[i + x]);
-            acc[x] = fmaf(s[i + x], qv[x], acc[x]);
-          }
+          for (int x = 0; x < VW; ++x)
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+              s[i + x][c] = fmaf(kw[x], kv[c], s[i + x][c]);
+              acc[c] = fmaf(s[i + x][c], qv[x], acc[c]);
+            }
         }
       }
-      float o = VW == 4 ? (acc[0] + acc[1]) + (acc[2] + acc[VW - 1]) : acc[0] + acc[1];
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      if (j == 0 && live) out[(size_t)(first + c0 + tt) * ((size_t)g.heads * g.vdim) + a * g.vdim + col] = o * qscale;
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 1);
+        acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 2);
+        acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 4);
+      }
+      if (j == 0) {
+        float* orow = out + (size_t)(first + c0 + tt) * ((size_t)g.heads * g.vdim) + a * g.vdim + col0 + cl;
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+          if (col0 + cl + c < g.vdim) orow[c] = acc[c] * qscale;
+      }
     }
     __syncthreads();   // the chunk has been consumed: its stage may be filled again
   }
-  if (live) {
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) {
-      const int d = i * SC_LANES + j;
-      if (d < g.dim) s_out[(size_t)d * g.vdim + col] = s[i];
-    }
+  for (int i = 0; i < DPT; ++i) {
+    const int d = i * SC_LANES + j;
+#pragma unroll
+    for (int c = 0; c < NC; ++c)
+      if (d < g.dim && col0 + cl + c < g.vdim) s_out[(size_t)d * g.vdim + col0 + cl + c] = s[i][c];
   }
 }
 
@@ -341,18 +369,18 @@ int launch_scan_rule(int dpt, dim3 grid, dim3 block, cudaStream_t s, const float
                      const float* decay, const float* beta, const StateGeom& g, float qscale, float* state, const int32_t* last_rows,
                      const int32_t* row_seq, const int32_t* row_first, const int32_t* row_end, const int32_t* positions, const int32_t* slots,
                      float* out, int cols) {
-#define B2_SCAN_CASE(D)                                                                                                                    \
-  case D:                                                                                                                                  \
-    B2_CUDA_OK(b2_launch(state_scan_kernel<D, RULE>, grid, block, 0, s, q, ldq, k, ldk, v, ldv, decay, beta, g, qscale, state, last_rows,  \
-                         row_seq, row_first, row_end, positions, slots, out, cols));                                                       \
+#define B2_SCAN_CASE(D, N)                                                                                                                    \
+  case D:                                                                                                                                     \
+    B2_CUDA_OK(b2_launch(state_scan_kernel<D, N, RULE>, grid, block, 0, s, q, ldq, k, ldk, v, ldv, decay, beta, g, qscale, state, last_rows,  \
+                         row_seq, row_first, row_end, positions, slots, out, cols));                                                          \
     return 0;
   switch (dpt) {
-    B2_SCAN_CASE(2)
-    B2_SCAN_CASE(4)
-    B2_SCAN_CASE(8)
-    B2_SCAN_CASE(16)
-    B2_SCAN_CASE(32)
-    B2_SCAN_CASE(64)
+    B2_SCAN_CASE(1, 4)
+    B2_SCAN_CASE(2, 4)
+    B2_SCAN_CASE(4, 4)
+    B2_SCAN_CASE(8, 4)
+    B2_SCAN_CASE(16, 4)
+    B2_SCAN_CASE(32, 2)
   }
 #undef B2_SCAN_CASE
   b2_set_error("state_scan: key width %d not built (at most 256)", g.dim);
@@ -392,12 +420,15 @@ int launch_state_scan(const float* q, int ldq, const float* k, int ldk, const fl
   if (portions <= 0) return 0;
   B2_REQUIRE(g.heads >= 1 && g.kv_heads >= 1 && g.heads % g.kv_heads == 0 && g.dim >= 1 && g.vdim >= 1, "state_scan: bad sizes");
   B2_REQUIRE(g.rule == STATE_RULE_DECAY || (g.rule == STATE_RULE_DELTA && beta != nullptr), "state_scan: rule %d", g.rule);
-  int dpt = 2;
+  int dpt = 1;
   while (dpt * SC_LANES < g.dim) dpt *= 2;
-  // as many columns per CTA as still leave two CTAs for every SM (a column's arithmetic does not depend on the tile it falls into)
-  int cols = std::min(SC_COLS, (g.vdim + 7) / 8 * 8);
-  while (cols > 16 && (long)portions * g.heads * ((g.vdim + cols - 1) / cols) < 2L * device_num_sms()) cols = (cols / 2 + 7) / 8 * 8;
-  const dim3 grid(portions, g.heads, (g.vdim + cols - 1) / cols), block(cols * SC_LANES);
+  B2_REQUIRE(dpt <= 32, "state_scan: key width %d not built (at most 256)", g.dim);
+  // a warp is four groups of eight lanes, a group owns nc neighbouring columns; as many columns per CTA (at most eight warps) as still
+  // leave two CTAs for every SM (a column's arithmetic does not depend on the tile it falls into)
+  const int nc = dpt >= 32 ? 2 : 4, step = 4 * nc;
+  int cols = std::min(32 * nc, (g.vdim + step - 1) / step * step);
+  while (cols > step && (long)portions * g.heads * ((g.vdim + cols - 1) / cols) < 2L * device_num_sms()) cols = (cols / 2 + step - 1) / step * step;
+  const dim3 grid(portions, g.heads, (g.vdim + cols - 1) / cols), block(cols / nc * SC_LANES);
   if (g.rule == STATE_RULE_DECAY)
     return launch_scan_rule<STATE_RULE_DECAY>(dpt, grid, block, s, q, ldq, k, ldk, v, ldv, decay, beta, g, qscale, state, last_rows, row_seq,
                                               row_first, row_end, positions, slots, out, cols);
