@@ -26,7 +26,8 @@
 //
 // Kernels:
 //   lowrank_act        y = act(W2 . lr + bias) for the low-rank second stages (decays, output gates), fp32
-//   conv_unit_finish   delta rule: causal convolution + silu on q | k | v, unit vectors, query scale, beta
+//   conv_unit_finish   delta rule: causal convolution + silu on q | k | v (a thread per channel), then unit vectors and the query scale
+//                      (a warp per head), beta
 //   conv_ring_store    the ring update, after every token of the step has read the ring
 //   state_scan         the recurrence
 //   state_out_gate     per-head RMS norm of the read-out with a gain, times the gate (silu or given), operand type out
@@ -86,51 +87,51 @@ __global__ void __launch_bounds__(256) lowrank_act_kernel(const float* __restric
   }
 }
 
-// One CTA per token, a warp per head unit (query/key heads, then value heads).  proj [T][ld] fp32 = q (kv_heads*dim) | k (kv_heads*dim) |
-// v (heads*vdim) | beta logits (heads) | ...; out [T][C] = the finished q | k | v, beta_out [T][heads].
-__global__ void __launch_bounds__(128) conv_unit_finish_kernel(const float* __restrict__ proj, int ld, StateGeom g, int taps,
+// A CTA takes `upc` head units of one token (query heads, key heads, value heads, in the order of the projection's columns): first every
+// thread convolves and activates channels of the CTA's range, then a warp per query / key head turns the head into a unit vector.
+// proj [T][ld] fp32 = q (kv_heads*dim) | k (kv_heads*dim) | v (heads*vdim) | beta logits (heads) | ...; out [T][C] = the finished q | k | v,
+// beta_out [T][heads].
+__global__ void __launch_bounds__(256) conv_unit_finish_kernel(const float* __restrict__ proj, int ld, StateGeom g, int taps,
                                                                const float* __restrict__ conv_w, const float* __restrict__ ring,
                                                                const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_first,
                                                                const int32_t* __restrict__ positions, const int32_t* __restrict__ slots,
-                                                               float unit_eps, float* __restrict__ out, float* __restrict__ beta_out) {
+                                                               float unit_eps, float* __restrict__ out, float* __restrict__ beta_out, int upc) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (slots[t] < 0) return;
   const int pos = positions[t];
   const int nqk = g.kv_heads * g.dim, nv = g.heads * g.vdim, C = 2 * nqk + nv;
+  const int units = 2 * g.kv_heads + g.heads, u_lo = blockIdx.y * upc, u_hi = min(units, u_lo + upc);
+  auto unit_c0 = [&](int u) { return u < 2 * g.kv_heads ? u * g.dim : 2 * nqk + (u - 2 * g.kv_heads) * g.vdim; };
+  const int c_lo = unit_c0(u_lo), c_hi = u_hi == units ? C : unit_c0(u_hi);
   const int back = t - row_first[t];
   const float* row = proj + (size_t)t * ld;
   const float* rg = ring + (size_t)row_seq[t] * taps * C;
   float* orow = out + (size_t)t * C;
-  const float qscale = rsqrtf((float)g.dim);
-  const int units = 2 * g.kv_heads + g.heads;
-  for (int u = warp; u < units; u += 4) {
-    const bool is_v = u >= 2 * g.kv_heads;
-    const int width = is_v ? g.vdim : g.dim;
-    const int c0 = is_v ? 2 * nqk + (u - 2 * g.kv_heads) * g.vdim : u * g.dim;
-    float ss = 0.f;
-    for (int i = lane; i < width; i += 32) {
-      const int c = c0 + i;
-      float acc = 0.f;
-      for (int j = 0; j < taps; ++j) {          // y_t = sum_j w[c][j] * x_(t - taps + 1 + j), the last column is the current token's
-        const int d = taps - 1 - j;
-        float xx = 0.f;
-        if (d <= back) xx = (row - (size_t)d * ld)[c];
-        else if (pos - d >= 0) xx = rg[(size_t)((pos - d) % taps) * C + c];
-        acc = fmaf(conv_w[(size_t)c * taps + j], xx, acc);
-      }
-      const float y = silu_f(acc);
-      orow[c] = y;   // (a lane reads back only what it wrote)
-      ss = fmaf(y, y, ss);
+  for (int c = c_lo + threadIdx.x; c < c_hi; c += 256) {
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {          // y_t = sum_j w[c][j] * x_(t - taps + 1 + j), the last column is the current token's
+      const int d = taps - 1 - j;
+      float xx = 0.f;
+      if (d <= back) xx = (row - (size_t)d * ld)[c];
+      else if (pos - d >= 0) xx = rg[(size_t)((pos - d) % taps) * C + c];
+      acc = fmaf(conv_w[(size_t)c * taps + j], xx, acc);
     }
-    if (!is_v) {
-      ss = warp_sum(ss);
-      const float r = (1.0f / sqrtf(ss + unit_eps)) * (u < g.kv_heads ? qscale : 1.0f);
-      for (int i = lane; i < width; i += 32) orow[c0 + i] *= r;
-    }
+    orow[c] = silu_f(acc);
   }
-  for (int a = threadIdx.x; a < g.heads; a += 128) beta_out[(size_t)t * g.heads + a] = sigmoid_f(row[C + a]);
+  __syncthreads();   // (the CTA reads back only what it wrote itself)
+  const float qscale = rsqrtf((float)g.dim);
+  for (int u = u_lo + warp; u < min(u_hi, 2 * g.kv_heads); u += 8) {
+    float* h = orow + u * g.dim;
+    float ss = 0.f;
+    for (int i = lane; i < g.dim; i += 32) ss = fmaf(h[i], h[i], ss);
+    ss = warp_sum(ss);
+    const float r = (1.0f / sqrtf(ss + unit_eps)) * (u < g.kv_heads ? qscale : 1.0f);
+    for (int i = lane; i < g.dim; i += 32) h[i] *= r;
+  }
+  if (blockIdx.y == 0)
+    for (int a = threadIdx.x; a < g.heads; a += 256) beta_out[(size_t)t * g.heads + a] = sigmoid_f(row[C + a]);
 }
 
 __global__ void __launch_bounds__(128) conv_ring_store_kernel(const float* __restrict__ proj, int ld, int C, int taps, float* __restrict__ ring,
@@ -406,8 +407,9 @@ int launch_conv_unit_finish(const float* proj, int ld, const StateGeom& g, int t
   if (T <= 0) return 0;
   B2_REQUIRE(taps >= 1 && conv_w && (ring || taps == 1) && row_seq && row_first && row_end, "conv_unit_finish: the convolution needs its weights and state");
   const int C = 2 * g.kv_heads * g.dim + g.heads * g.vdim;
-  B2_CUDA_OK(b2_launch(conv_unit_finish_kernel, dim3(T), dim3(128), 0, s, proj, ld, g, taps, conv_w, (const float*)ring, row_seq, row_first,
-                       positions, slots, unit_eps, out, beta_out));
+  const int units = 2 * g.kv_heads + g.heads, upc = T >= 256 ? units : std::max(1, (units + 15) / 16);   // few tokens: up to sixteen CTAs each
+  B2_CUDA_OK(b2_launch(conv_unit_finish_kernel, dim3(T, (units + upc - 1) / upc), dim3(256), 0, s, proj, ld, g, taps, conv_w, (const float*)ring, row_seq,
+                       row_first, positions, slots, unit_eps, out, beta_out, upc));
   if (taps > 1)
     B2_CUDA_OK(b2_launch(conv_ring_store_kernel, dim3(T), dim3(128), 0, s, proj, ld, C, taps, ring, row_seq, row_end, positions, slots));
   return 0;

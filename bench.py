@@ -471,7 +471,8 @@ def bumalix_model_cfg(width, heads, inter, layers=4, vocab=32000):
     par = {"left": {"heads": heads, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 512}},
            "right": {"heads": heads // 2, "dim": 128, "vdim": 256, "tau": 16.0}}
     dlt = {"heads": heads, "kv_heads": heads, "dim": 128, "vdim": 128, "conv": 4}
-    dense = {"kind": "dense", "ff": (3 * inter // 2 + 255) // 256 * 256}
+    dense = {"kind": "dense", "ff": min((3 * inter // 2 + 255) // 256 * 256, 16384)}   # two matrices with the parameters of Qwen3's three (a decode step's
+                                                                                       # weight-streaming products stage rows of at most 16384 numbers)
     moe = {"kind": "moe", "expert": {"ff": (inter // 3 + 63) // 64 * 64}, "router": {"experts": 16, "top": 2}, "shared": {"ff": (inter // 3 + 63) // 64 * 64}}
     ls = [{"type": "channel_delta" if i % 2 else "parallel", "mixer": dlt if i % 2 else par, "mlp": moe if i % 4 in (1, 2) else dense} for i in range(layers)]
     return {"architecture": "Bumalix", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
