@@ -1839,7 +1839,10 @@ int list_tensor(b2_engine* e, const std::string& name, const void* host, size_t 
   if (name == "head") { B2_TRY(want((size_t)c.vocab * W)); return done(put_operand(e, e->l_head, 0, src, (size_t)c.vocab * W)); }
   if (name == "embed.norm") { B2_TRY(want(W)); return done(put_f32(e->l_embed_gain, src, W, 1.0f)); }
   if (name == "final.norm") { B2_TRY(want(W)); return done(put_f32(e->l_final_gain, src, W, c.arch == B2_ARCH_LERASUN ? 1.0f : 0.0f)); }
-  if (c.arch == B2_ARCH_BUMALIX && name == "loop.in" && e->l_loop_in) { B2_TRY(want(W * 2 * W)); return done(put_operand(e, e->l_loop_in, 0, src, W * 2 * W)); }
+  if (c.arch == B2_ARCH_BUMALIX && name == "loop.in") {   // (a checkpoint may carry it although the config loops over nothing: nothing then uses it)
+    B2_TRY(want(W * 2 * W));
+    return done(e->l_loop_in ? put_operand(e, e->l_loop_in, 0, src, W * 2 * W) : 0);
+  }
   size_t dot = name.find('.');
   if (name.size() < 3 || name[0] != 'l' || dot == std::string::npos || dot < 2) {
     b2_set_error("unknown tensor name %s", name.c_str());
