@@ -335,6 +335,8 @@ struct b2_engine {
   void *l_loop_in = nullptr, *l_cat = nullptr, *l_av2 = nullptr;   // W_in [W][2W]; its input [x | x0]; the second mixer's gated read-out
   float *l_dec = nullptr, *l_beta = nullptr, *l_gate = nullptr, *l_so = nullptr, *l_mix2 = nullptr, *l_ffd = nullptr, *l_slot_scale = nullptr;
   size_t l_qd_cols = 0;
+  cudaStream_t l_side[2] = {nullptr, nullptr};   // short steps: the second mixer and the feed-forward of a layer run beside the first mixer
+  cudaEvent_t l_ev[4] = {nullptr, nullptr, nullptr, nullptr};
 };
 
 namespace {
@@ -895,7 +897,8 @@ bool list_use_tc() {
   static const bool use_tc = [] { const char* v = getenv("B2_LIST_TC"); return !(v && *v == '0'); }();
   return use_tc;
 }
-int list_dense(b2_engine* e, const void* A, const void* Wt, float* C, int M, int N, int K, float alpha) {
+int list_dense(b2_engine* e, const void* A, const void* Wt, float* C, int M, int N, int K, float alpha, cudaStream_t stream = nullptr) {
+  cudaStream_t ls = stream ? stream : e->stream;
   const int f = e->f32 ? 1 : 0;
   if (list_use_tc() && !f && alpha == 1.f && M > 64 && N >= 128 && K % 64 == 0) {
     TcGemmArgs a;
@@ -908,11 +911,11 @@ int list_dense(b2_engine* e, const void* A, const void* Wt, float* C, int M, int
     a.x_raw = A;
     a.argmax_packed = nullptr;
     a.epilogue = TC_EPI_F32_PARTIAL;
-    return launch_linear_tc(a, e->stream);
+    return launch_linear_tc(a, ls);
   }
   AnyGemm a;
   a.A = A; a.W = Wt; a.C = C; a.M = M; a.N = N; a.K = K; a.lda = K; a.ldw = K; a.ldc = N; a.alpha = alpha;
-  return launch_gemm_any(a, f, f, 1, 1, 0, e->stream);
+  return launch_gemm_any(a, f, f, 1, 1, 0, ls);
 }   // (token, choice) pairs of a step from which the experts' products go expert by expert to the tcgen05 kernel
 
 int forward_list(b2_engine* e, int T, int ntiles, int nlast) {
@@ -1194,7 +1197,25 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
     if ((e->debug_flags & 1) && e->dbg_hidden_f32 != nullptr && T <= e->dbg_cap_tokens && slot < e->dbg_slots)
       cudaMemcpyAsync(e->dbg_hidden_f32 + (size_t)slot * e->dbg_cap_tokens * W, e->l_h, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st);
   };
-  auto dense = [&](const void* A, const void* Wt, float* C, int M, int N, int K) -> int { return list_dense(e, A, Wt, C, M, N, K, 1.f); };
+  // Short steps (a decode step, a few tokens of prompts) are chains of small launches: a layer's second mixer and its feed-forward then
+  // run on streams of their own beside the first mixer and meet again at the kernel that adds the branches into the stream (inside a
+  // captured step these become parallel branches of the graph).  Profiled and debugged steps stay on one stream.
+  const bool multi = T <= 256 && !e->profiling && !(e->debug_flags & 1) && e->skip_mask == 0 && e->l_side[0] != nullptr;
+  cudaStream_t sB = multi ? e->l_side[0] : st, sF = multi ? e->l_side[1] : st;
+  auto fork = [&](cudaEvent_t ev, cudaStream_t to) -> int {     // `to` continues from this point of the main stream
+    if (!multi) return 0;
+    B2_CUDA_OK(cudaEventRecord(ev, st));
+    B2_CUDA_OK(cudaStreamWaitEvent(to, ev, 0));
+    return 0;
+  };
+  auto join = [&](cudaEvent_t ev, cudaStream_t from) -> int {   // the main stream waits for what `from` has been given
+    if (!multi) return 0;
+    B2_CUDA_OK(cudaEventRecord(ev, from));
+    B2_CUDA_OK(cudaStreamWaitEvent(st, ev, 0));
+    return 0;
+  };
+  auto first_on = [&](cudaStream_t) { if (multi) b2_pdl_skip_next(); };   // behind a cross-stream edge: an ordinary, full dependency
+  auto dense = [&](const void* A, const void* Wt, float* C, int M, int N, int K, cudaStream_t s_) -> int { return list_dense(e, A, Wt, C, M, N, K, 1.f, s_); };
   {
     KL k(e, B2K_EMBED);
     if (!k.skip()) B2_TRY(launch_embed_scaled(e->d_tokens, e->l_embed, f, c.embed_scale != 0.f ? c.embed_scale : 1.f, e->l_h, T, W, c.vocab, st));
@@ -1219,18 +1240,21 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
         if (!k.skip()) B2_TRY(launch_store_rows(e->l_h, e->l_cat, f, 2 * W, 0, T, W, st));
       }
       KL k(e, B2K_GEMM_O);
-      if (!k.skip()) B2_TRY(dense(e->l_cat, e->l_loop_in, e->l_h, T, W, 2 * W));
+      if (!k.skip()) B2_TRY(dense(e->l_cat, e->l_loop_in, e->l_h, T, W, 2 * W, st));
       have_norm = false;
     }
     if (!have_norm) {
       KL k(e, B2K_NORM);
       if (!k.skip()) B2_TRY(launch_group_norm(e->l_h, L.gain1, e->l_x1, f, T, W, 1, c.rms_eps, nullptr, st));
     }
+    const bool has_ff = sp.ff != B2_FF_NONE;
+    if (has_ff) B2_TRY(fork(e->l_ev[0], sF));      // the feed-forward needs the norm output only
     {
       KL k(e, B2K_GEMM_QKV);
-      if (!k.skip()) B2_TRY(dense(e->l_x1, L.wqd, e->l_qd, T, L.nqd, W));
+      if (!k.skip()) B2_TRY(dense(e->l_x1, L.wqd, e->l_qd, T, L.nqd, W, st));
     }
     const bool two = sp.mixer == B2_MIXER_WINDOW_AND_STATE;
+    if (two) B2_TRY(fork(e->l_ev[1], sB));         // the state mixer reads its part of the projection
     if (two) {
       HeadsGeom g{sp.heads, sp.kv_heads, sp.dim, sp.vdim, 0, 0.f, sp.scale, c.rms_eps, 0, 0, 0, 0.f, sp.window, 0, 0, 0};
       char* kc = e->regions[R.k_region].base;
@@ -1246,27 +1270,28 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
       }
       {
         KL k(e, B2K_GEMM_O);
-        if (!k.skip()) B2_TRY(dense(e->l_av, L.wo, e->l_mix, T, W, sp.heads * sp.vdim));
+        if (!k.skip()) B2_TRY(dense(e->l_av, L.wo, e->l_mix, T, W, sp.heads * sp.vdim, st));
       }
       const StateGeom sg{sp.s_heads, sp.s_heads, sp.s_dim, sp.s_vdim, STATE_RULE_DECAY};
+      first_on(sB);
       {
         KL k(e, B2K_ACT);   // decay per key channel: sigmoid(A2 (A1 n) + b)^(1 / tau)
         if (!k.skip()) B2_TRY(launch_lowrank_act(e->l_qd, L.nqd, L.n_fixed, L.rank_a, L.a2, L.a2_bias, LOWRANK_DECAY_SIGMOID_POW, 1.0f / sp.s_tau, nullptr, 0,
-                                                 e->l_dec, T, sp.s_heads * sp.s_dim, st));
+                                                 e->l_dec, T, sp.s_heads * sp.s_dim, sB));
       }
       {
         KL k(e, B2K_CHAIN);
         if (!k.skip()) B2_TRY(launch_state_scan(e->l_qd + L.off_sq, L.nqd, e->l_qd + L.off_sk, L.nqd, e->l_qd + L.off_sv, L.nqd, e->l_dec, nullptr, sg,
                                                 1.0f / sqrtf((float)sp.s_dim), R.state, portions, last_rows, e->d_row_seq, e->d_row_first, e->d_row_end,
-                                                e->d_positions, e->d_slots, e->l_so, st));
+                                                e->d_positions, e->d_slots, e->l_so, sB));
       }
       {
         KL k(e, B2K_ACT);
-        if (!k.skip()) B2_TRY(launch_state_out_gate(e->l_so, L.head_gain, e->l_qd + L.off_sg, L.nqd, 1, e->l_av2, f, sp.s_heads, sp.s_vdim, c.rms_eps, T, st));
+        if (!k.skip()) B2_TRY(launch_state_out_gate(e->l_so, L.head_gain, e->l_qd + L.off_sg, L.nqd, 1, e->l_av2, f, sp.s_heads, sp.s_vdim, c.rms_eps, T, sB));
       }
       {
         KL k(e, B2K_GEMM_O);
-        if (!k.skip()) B2_TRY(dense(e->l_av2, L.wo2, e->l_mix2, T, W, sp.s_heads * sp.s_vdim));
+        if (!k.skip()) B2_TRY(dense(e->l_av2, L.wo2, e->l_mix2, T, W, sp.s_heads * sp.s_vdim, sB));
       }
     } else {
       const StateGeom sg{sp.heads, sp.kv_heads, sp.dim, sp.vdim, STATE_RULE_DELTA};
@@ -1296,23 +1321,24 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
       }
       {
         KL k(e, B2K_GEMM_O);
-        if (!k.skip()) B2_TRY(dense(e->l_av, L.wo, e->l_mix, T, W, sp.heads * sp.vdim));
+        if (!k.skip()) B2_TRY(dense(e->l_av, L.wo, e->l_mix, T, W, sp.heads * sp.vdim, st));
       }
     }
     const float* d1 = nullptr;
+    if (has_ff) first_on(sF);
     const float* yr = nullptr;
     if (sp.ff == B2_FF_POLYNORM) {
       {
         KL k(e, B2K_GEMM_GATEUP);
-        if (!k.skip()) B2_TRY(dense(e->l_x1, L.up, e->l_upf, T, sp.ff_dim, W));
+        if (!k.skip()) B2_TRY(dense(e->l_x1, L.up, e->l_upf, T, sp.ff_dim, W, sF));
       }
       {
         KL k(e, B2K_ACT);
-        if (!k.skip()) B2_TRY(launch_poly_norm(e->l_upf, L.poly, e->l_act, f, T, sp.ff_dim, c.rms_eps, st));
+        if (!k.skip()) B2_TRY(launch_poly_norm(e->l_upf, L.poly, e->l_act, f, T, sp.ff_dim, c.rms_eps, sF));
       }
       {
         KL k(e, B2K_GEMM_DOWN);
-        if (!k.skip()) B2_TRY(dense(e->l_act, L.down, e->l_ffd, T, W, sp.ff_dim));
+        if (!k.skip()) B2_TRY(dense(e->l_act, L.down, e->l_ffd, T, W, sp.ff_dim, sF));
       }
       d1 = e->l_ffd;
     } else if (sp.ff == B2_FF_SCALED_GATED_EXPERTS) {
@@ -1320,19 +1346,19 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
       const int F = sp.ff_dim, pairs = T * sp.top;
       {
         KL k(e, B2K_ACT);
-        if (!k.skip()) B2_TRY(launch_route(e->l_x1, f, L.router, nullptr, rg, e->l_idx, e->l_rw, T, W, st));
+        if (!k.skip()) B2_TRY(launch_route(e->l_x1, f, L.router, nullptr, rg, e->l_idx, e->l_rw, T, W, sF));
       }
       {
         KL k(e, B2K_MISC);
         if (!k.skip()) {
-          B2_TRY(launch_route_permute(e->l_idx, T, sp.top, sp.experts, e->l_offsets, e->l_offsets_stride, e->l_slot_token, e->l_pair_slot, st));
-          B2_TRY(launch_route_slot_weights(e->l_rw, e->l_pair_slot, e->l_slot_scale, pairs, st));
+          B2_TRY(launch_route_permute(e->l_idx, T, sp.top, sp.experts, e->l_offsets, e->l_offsets_stride, e->l_slot_token, e->l_pair_slot, sF));
+          B2_TRY(launch_route_slot_weights(e->l_rw, e->l_pair_slot, e->l_slot_scale, pairs, sF));
         }
       }
       // The weight multiplies the expert's input: gate and up are linear in it, so it is applied to their fp32 sums inside the
       // activation.  Prompt-sized bf16 steps run expert by expert on the tcgen05 projection kernel (rows gathered into expert
       // order, slot ranges read back); everything else as ragged groups.
-      const bool tc_experts = use_tc && !f && ntiles > 0 && e->l_xperm != nullptr && pairs >= LIST_TC_EXPERT_ROWS && W % 64 == 0 && F % 64 == 0 &&
+      const bool tc_experts = !multi && use_tc && !f && ntiles > 0 && e->l_xperm != nullptr && pairs >= LIST_TC_EXPERT_ROWS && W % 64 == 0 && F % 64 == 0 &&
                               W >= 128 && F >= 64 && e->skip_mask == 0;
       if (tc_experts) {
         B2_CUDA_OK(cudaMemcpyAsync(e->h_offsets, e->l_offsets, (size_t)(sp.experts + 1) * 4, cudaMemcpyDeviceToHost, st));
@@ -1348,7 +1374,7 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
           for (int x = 0; x < sp.experts; ++x)
             if (off[x + 1] > off[x])
               B2_TRY(dense(e->l_xperm + (size_t)off[x] * W, (const bf16*)L.up + (size_t)x * 2 * F * W, e->l_upf + (size_t)off[x] * 2 * F, off[x + 1] - off[x],
-                           2 * F, W));
+                           2 * F, W, st));
         }
         {
           KL k(e, B2K_ACT);
@@ -1359,13 +1385,13 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
           for (int x = 0; x < sp.experts; ++x)
             if (off[x + 1] > off[x])
               B2_TRY(dense((const bf16*)e->l_act + (size_t)off[x] * F, (const bf16*)L.down + (size_t)x * W * F, e->l_y + (size_t)off[x] * W,
-                           off[x + 1] - off[x], W, F));
+                           off[x + 1] - off[x], W, F, st));
         }
       } else {
         const int max_tiles = std::min(e->l_tiles_cap, (pairs + any_gemm_tile_rows() - 1) / any_gemm_tile_rows() + sp.experts);
         if (pairs > any_gemm_ragged_rows_limit() || W > 16384 || 2 * F > 16384) {
           KL k(e, B2K_MISC);
-          if (!k.skip()) B2_TRY(launch_ragged_tiles(e->l_offsets, sp.experts, e->l_tile_group, e->l_tile_row0, e->l_ntiles, max_tiles, st));
+          if (!k.skip()) B2_TRY(launch_ragged_tiles(e->l_offsets, sp.experts, e->l_tile_group, e->l_tile_row0, e->l_ntiles, max_tiles, sF));
         }
         AnyGemm a;
         a.tile_group = e->l_tile_group; a.tile_row0 = e->l_tile_row0; a.n_tiles = e->l_ntiles; a.group_offsets = e->l_offsets;
@@ -1373,36 +1399,39 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
           KL k(e, B2K_GEMM_GATEUP);  // gate | up of every (token, choice) pair in expert order, fp32 sums
           a.A = e->l_x1; a.a_rows = e->l_slot_token; a.W = L.up; a.C = e->l_upf; a.N = 2 * F; a.K = W; a.lda = W; a.ldw = W; a.ldc = 2 * F;
           a.w_bs = (long)2 * F * W; a.epilogue = ANY_EPI_STORE;
-          if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, max_tiles, st, pairs, sp.experts));
+          if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, max_tiles, sF, pairs, sp.experts));
         }
         {
           KL k(e, B2K_ACT);
-          if (!k.skip()) B2_TRY(launch_silu_gate(e->l_upf, e->l_slot_scale, nullptr, e->l_act, f, pairs, F, st));
+          if (!k.skip()) B2_TRY(launch_silu_gate(e->l_upf, e->l_slot_scale, nullptr, e->l_act, f, pairs, F, sF));
         }
         {
           KL k(e, B2K_GEMM_DOWN);
           a.A = e->l_act; a.a_rows = nullptr; a.W = L.down; a.C = e->l_y; a.N = W; a.K = F; a.lda = F; a.ldw = F; a.ldc = W;
           a.w_bs = (long)W * F; a.epilogue = ANY_EPI_STORE;
-          if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, max_tiles, st, pairs, sp.experts));
+          if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, max_tiles, sF, pairs, sp.experts));
         }
       }
       yr = e->l_y;
       if (sp.shared_ff > 0) {
         {
           KL k(e, B2K_GEMM_GATEUP);
-          if (!k.skip()) B2_TRY(dense(e->l_x1, L.sh_up, e->l_upf, T, 2 * sp.shared_ff, W));
+          if (!k.skip()) B2_TRY(dense(e->l_x1, L.sh_up, e->l_upf, T, 2 * sp.shared_ff, W, sF));
         }
         {
           KL k(e, B2K_ACT);
-          if (!k.skip()) B2_TRY(launch_silu_gate(e->l_upf, nullptr, nullptr, e->l_act, f, T, sp.shared_ff, st));
+          if (!k.skip()) B2_TRY(launch_silu_gate(e->l_upf, nullptr, nullptr, e->l_act, f, T, sp.shared_ff, sF));
         }
         {
           KL k(e, B2K_GEMM_DOWN);
-          if (!k.skip()) B2_TRY(dense(e->l_act, L.sh_down, e->l_ffd, T, W, sp.shared_ff));
+          if (!k.skip()) B2_TRY(dense(e->l_act, L.sh_down, e->l_ffd, T, W, sp.shared_ff, sF));
         }
         d1 = e->l_ffd;
       }
     }
+    if (two) B2_TRY(join(e->l_ev[2], sB));
+    if (has_ff) B2_TRY(join(e->l_ev[3], sF));
+    if (two || has_ff) first_on(st);
     {
       KL k(e, B2K_NORM);  // h += (mixer + ff); the next layer's norm output, unless the loop's input mix comes first
       const bool next_plain = r + 1 < e->runs.size() && !e->runs[r + 1].pass_start && e->skip_mask == 0;
@@ -1420,7 +1449,7 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
   }
   {
     KL k(e, B2K_LMHEAD);
-    if (!k.skip()) B2_TRY(dense(e->l_xl, e->l_head, e->l_logits, nlast, c.vocab, W));
+    if (!k.skip()) B2_TRY(dense(e->l_xl, e->l_head, e->l_logits, nlast, c.vocab, W, st));
   }
   {
     KL k(e, B2K_MISC);
@@ -2277,6 +2306,8 @@ int state_engine_alloc(b2_engine* e) {
   }
   e->l_has_state = true;
   e->dbg_slots = (int)e->runs.size() + 1;
+  for (auto& sd : e->l_side) B2_CUDA_OK(cudaStreamCreateWithFlags(&sd, cudaStreamNonBlocking));
+  for (auto& ev : e->l_ev) B2_CUDA_OK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
   // ---- activations ----
   e->cap_tokens = ((std::max(c.max_batch_tokens, c.max_seqs) + 255) / 256) * 256;
   const size_t Tc = e->cap_tokens;
@@ -3230,6 +3261,10 @@ extern "C" void b2_engine_free(b2_engine* e) {
   for (auto& R : e->runs) {
     F(R.state); F(R.ring);
   }
+  for (auto& ev : e->l_ev)
+    if (ev) cudaEventDestroy(ev);
+  for (auto& sd : e->l_side)
+    if (sd) cudaStreamDestroy(sd);
   F(e->l_loop_in); F(e->l_cat); F(e->l_av2); F(e->l_dec); F(e->l_beta); F(e->l_gate); F(e->l_so); F(e->l_mix2); F(e->l_ffd); F(e->l_slot_scale);
   if (e->ev_fork) cudaEventDestroy(e->ev_fork);
   if (e->ev_join) cudaEventDestroy(e->ev_join);
