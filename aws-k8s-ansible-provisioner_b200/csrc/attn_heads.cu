@@ -175,7 +175,8 @@ __global__ void __launch_bounds__(128) heads_finish_kernel(const float* __restri
 template <typename TC>
 __global__ void __launch_bounds__(128) heads_finish_rownorm_kernel(const float* __restrict__ proj, int ld, HeadsGeom g, const float* __restrict__ bias,
                                                                    const float* __restrict__ qk_gain, const int32_t* __restrict__ slots,
-                                                                   float* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache) {
+                                                                   float* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache,
+                                                                   bf16* __restrict__ q_bf16) {
   __shared__ float red[2][4];
   pdl_wait();
   pdl_launch_dependents();
@@ -202,6 +203,13 @@ __global__ void __launch_bounds__(128) heads_finish_rownorm_kernel(const float* 
   __syncthreads();
   const float rq = 1.0f / sqrtf((red[0][0] + red[0][1] + red[0][2] + red[0][3]) / (float)nq + g.eps);
   const float rk = 1.0f / sqrtf((red[1][0] + red[1][1] + red[1][2] + red[1][3]) / (float)nk + g.eps);
+  if (g.swizzled) {   // the page layout of the GQA kernels (128-wide heads), queries as bf16
+    for (int i = threadIdx.x; i < nq; i += 128) q_bf16[(size_t)t * nq + i] = __float2bfloat16_rn((row[i] + (bias ? bias[i] : 0.f)) * rq * qk_gain[i]);
+    for (int i = threadIdx.x; i < nk; i += 128)
+      stf(k_cache + swizzled_index(slot, i >> 7, g.kv_heads, i & 127), (row[nq + i] + (bias ? bias[nq + i] : 0.f)) * rk * qk_gain[nq + i]);
+    for (int i = threadIdx.x; i < nv; i += 128) stf(v_cache + swizzled_index(slot, i >> 7, g.kv_heads, i & 127), row[nq + nk + i] + (bias ? bias[nq + nk + i] : 0.f));
+    return;
+  }
   for (int i = threadIdx.x; i < nq; i += 128) q_out[(size_t)t * nq + i] = (row[i] + (bias ? bias[i] : 0.f)) * rq * qk_gain[i];
   for (int i = threadIdx.x; i < nk; i += 128) stf(k_cache + (size_t)slot * nk + i, (row[nq + i] + (bias ? bias[nq + i] : 0.f)) * rk * qk_gain[nq + i]);
   for (int i = threadIdx.x; i < nv; i += 128) stf(v_cache + (size_t)slot * nv + i, row[nq + nk + i] + (bias ? bias[nq + nk + i] : 0.f));
@@ -769,13 +777,16 @@ int launch_heads_finish(const float* proj, int ld, const HeadsGeom& g, const flo
 }
 
 int launch_heads_finish_rownorm(const float* proj, int ld, const HeadsGeom& g, const float* bias, const float* qk_gain, const int32_t* slots,
-                                float* q_out, void* k_cache, void* v_cache, int cache_f32, int T, cudaStream_t s) {
+                                float* q_out, void* k_cache, void* v_cache, int cache_f32, int T, cudaStream_t s, void* q_bf16) {
   if (T <= 0) return 0;
   B2_REQUIRE(qk_gain != nullptr, "heads_finish_rownorm: the row norms need their gains");
+  B2_REQUIRE(!g.swizzled || (!cache_f32 && g.dim == 128 && g.vdim == 128 && q_bf16 != nullptr), "heads_finish_rownorm: the swizzled page layout is bf16, 128 wide");
   if (cache_f32)
-    B2_CUDA_OK(b2_launch(heads_finish_rownorm_kernel<float>, dim3(T), dim3(128), 0, s, proj, ld, g, bias, qk_gain, slots, q_out, (float*)k_cache, (float*)v_cache));
+    B2_CUDA_OK(b2_launch(heads_finish_rownorm_kernel<float>, dim3(T), dim3(128), 0, s, proj, ld, g, bias, qk_gain, slots, q_out, (float*)k_cache, (float*)v_cache,
+                         (bf16*)nullptr));
   else
-    B2_CUDA_OK(b2_launch(heads_finish_rownorm_kernel<bf16>, dim3(T), dim3(128), 0, s, proj, ld, g, bias, qk_gain, slots, q_out, (bf16*)k_cache, (bf16*)v_cache));
+    B2_CUDA_OK(b2_launch(heads_finish_rownorm_kernel<bf16>, dim3(T), dim3(128), 0, s, proj, ld, g, bias, qk_gain, slots, q_out, (bf16*)k_cache, (bf16*)v_cache,
+                         (bf16*)q_bf16));
   return 0;
 }
 

@@ -1256,14 +1256,24 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
     const bool two = sp.mixer == B2_MIXER_WINDOW_AND_STATE;
     if (two) B2_TRY(fork(e->l_ev[1], sB));         // the state mixer reads its part of the projection
     if (two) {
-      HeadsGeom g{sp.heads, sp.kv_heads, sp.dim, sp.vdim, 0, 0.f, sp.scale, c.rms_eps, 0, 0, 0, 0.f, sp.window, 0, 0, 0};
+      HeadsGeom g{sp.heads, sp.kv_heads, sp.dim, sp.vdim, 0, 0.f, sp.scale, c.rms_eps, 0, 0, 0, 0.f, sp.window, 0, 0, L.gqa_tc ? 1 : 0};
       char* kc = e->regions[R.k_region].base;
       char* vc = e->regions[R.v_region].base;
       {
         KL k(e, B2K_ROPE_KV);
-        if (!k.skip()) B2_TRY(launch_heads_finish_rownorm(e->l_qd, L.nqd, g, L.qkv_bias, L.qk_gain, e->d_slots, e->l_q, kc, vc, f, T, st));
+        if (!k.skip()) B2_TRY(launch_heads_finish_rownorm(e->l_qd, L.nqd, g, L.qkv_bias, L.qk_gain, e->d_slots, e->l_q, kc, vc, f, T, st, L.gqa_tc ? e->l_qb : nullptr));
       }
-      {
+      if (L.gqa_tc) {   // the framework's GQA kernels: tcgen05 for prompt portions, the page-balanced stream for decode steps
+        KL k(e, ntiles > 0 ? B2K_MISC : B2K_ATTN_DECODE);
+        if (!k.skip()) {
+          if (ntiles > 0)
+            B2_TRY(launch_attn_prefill_tc(e->l_qb, (const bf16*)kc, (const bf16*)vc, e->num_blocks, e->d_block_table, e->bt_stride, e->d_tiles, ntiles,
+                                          (bf16*)e->l_av, sp.heads, sp.kv_heads, 128, c.block_size, st, sp.scale, sp.window, 0));
+          else
+            B2_TRY(launch_attn_decode(e->l_qb, (const bf16*)kc, (const bf16*)vc, e->d_block_table, e->bt_stride, e->d_seq_lens, e->attn_scratch, (bf16*)e->l_av, T,
+                                      sp.heads, sp.kv_heads, 128, c.block_size, st, sp.scale, sp.window, 0));
+        }
+      } else {
         KL k(e, ntiles > 0 ? B2K_MISC : B2K_ATTN_DECODE);
         if (!k.skip()) B2_TRY(launch_heads_attention(e->l_q, kc, vc, f, g, e->d_block_table, e->bt_stride, c.block_size, tiles, ntiles, e->d_positions,
                                                      e->d_seq_lens, e->l_av, f, T, st));
@@ -2201,7 +2211,7 @@ int state_engine_alloc(b2_engine* e) {
   const bool looped = c.loop_times > 0 && c.loop_stop > c.loop_start;
   if (looped) B2_TRY(xalloc(&e->l_loop_in, W * 2 * W));
   e->ll.resize(c.num_layers);
-  size_t max_q = 1, max_dec = 1, max_hv = 1, max_hv2 = 1, max_heads = 1, max_up = 1, max_act = 1;
+  size_t max_q = 1, max_dec = 1, max_hv = 1, max_hv2 = 1, max_heads = 1, max_up = 1, max_act = 1, gqa_scratch = 0;
   int max_top = 1, max_exp = 1;
   for (int l = 0; l < c.num_layers; ++l) {
     ListLayer& L = e->ll[l];
@@ -2231,6 +2241,12 @@ int state_engine_alloc(b2_engine* e) {
       B2_TRY(falloc(&L.a2_bias, (size_t)sp.s_heads * sp.s_dim));
       B2_TRY(falloc(&L.out_gain_l, W));
       B2_TRY(falloc(&L.out_gain_r, W));
+      static const bool use_gqa_tc = [] { const char* v = getenv("B2_HEADS_GQA_TC"); return !(v && *v == '0'); }();
+      // the geometry the engine's GQA attention kernels are built for (they take a sliding window as an argument): such a layer keeps its
+      // caches in their page layout and runs on them
+      L.gqa_tc = use_gqa_tc && !e->f32 && sp.dim == 128 && sp.vdim == 128 && sp.heads == 2 * sp.kv_heads && c.block_size == 16 &&
+                 (c.max_model_len + 15) / 16 <= 1024 && (long)bucket_batch(c.max_seqs) * sp.kv_heads <= 4096;
+      if (L.gqa_tc) gqa_scratch = std::max(gqa_scratch, attn_decode_scratch_floats(bucket_batch(c.max_seqs), sp.heads, sp.kv_heads, 128));
       max_q = std::max(max_q, (size_t)L.nq);
       max_dec = std::max(max_dec, (size_t)sp.s_heads * sp.s_dim);
       max_hv = std::max({max_hv, (size_t)sp.heads * sp.vdim, (size_t)sp.s_heads * sp.s_vdim});
@@ -2322,6 +2338,12 @@ int state_engine_alloc(b2_engine* e) {
   };
   B2_TRY(dalloc(&e->l_h, Tc * W));
   B2_TRY(dalloc(&e->l_q, Tc * max_q));
+  if (gqa_scratch > 0) {
+    B2_TRY(dalloc(&e->l_qb, Tc * max_q));
+    e->attn_scratch_floats = gqa_scratch;
+    B2_TRY(dalloc(&e->attn_scratch, gqa_scratch));
+    B2_CUDA_OK(cudaMemset(e->attn_scratch, 0, gqa_scratch * sizeof(float)));   // arrival counters start at zero
+  }
   B2_TRY(dalloc(&e->l_dec, Tc * max_dec));
   B2_TRY(dalloc(&e->l_beta, Tc * max_heads));
   B2_TRY(dalloc(&e->l_gate, Tc * max_hv));

@@ -312,9 +312,10 @@ int launch_heads_attention(const float* q, const void* k_cache, const void* v_ca
 // out[t][a][d] = sigmoid(gate[t*gate_ld + a]) * sum_b talk[a][b] * cross[t][b][(a / (heads/kv_heads)) * vdim + d]; gate may be null
 // What follows a fused, biased q | k | v projection when q and k are RMS-normed over the WHOLE row (all heads at once) with a gain per
 // entry: proj [T][ld] fp32 = q (heads*dim) | k (kv_heads*dim) | v (kv_heads*vdim) | anything else; bias [nq + nk + nv] or null;
-// qk_gain [nq + nk].  Writes q_out [T][heads*dim] fp32 and the token's K and V cache rows (plain layout).
+// qk_gain [nq + nk].  Writes q_out [T][heads*dim] fp32 and the token's K and V cache rows (plain layout); with g.swizzled the rows go into
+// the GQA kernels' page layout and the queries out as bf16 (q_bf16) instead.
 int launch_heads_finish_rownorm(const float* proj, int ld, const HeadsGeom& g, const float* bias, const float* qk_gain, const int32_t* slots,
-                                float* q_out, void* k_cache, void* v_cache, int cache_f32, int T, cudaStream_t s);
+                                float* q_out, void* k_cache, void* v_cache, int cache_f32, int T, cudaStream_t s, void* q_bf16 = nullptr);
 int launch_talk_gate(const float* cross, const float* talk, const float* gate, int gate_ld, void* out, int out_f32, int heads, int kv_heads,
                      int vdim, int T, cudaStream_t s);
 

@@ -230,6 +230,47 @@ def test_bf16_long_step_runs_the_experts_one_by_one():
     assert err(lw[:len(range(0, 200, 7))], ref[0:200:7]) < BF16_BAR
 
 
+def test_bf16_pairs_of_128_wide_heads():
+    """bf16, softmax mixers with 128-wide heads in groups of two: their caches take the page layout of the engine's GQA attention kernels
+    (tensor-core prompt pass, page-balanced decode pass), with this family's window as their argument; a layer of another geometry keeps the
+    plain layout beside them.  A long prompt, portions that end inside tiles and pages, single tokens inside a mixed step, a decode batch of
+    unequal lengths past the window's edge."""
+    cfg = model([(par(4, 2, 128, 128, 128 ** -0.5, 50, 2, 16, 32, 8.0), dense(128)), (delta(2, 1, 32, 32, 3), dense(64)),
+                 (par(2, 1, 128, 128, 0.1, None, 1, 32, 32, 4.0), None), (par(2, 2, 128, 128, 0.1, 30, 1, 32, 32, 4.0), dense(64))], vocab=300, width=128,
+                loop=(1, 3, 2))
+    w = random_weights(cfg, seed=61)
+    prompts = [tokens(cfg, 330, 62), tokens(cfg, 75, 63)]
+    refs = [ref_logits(cfg, w, p) for p in prompts]
+    with engine(cfg, w, f32=False) as e:
+        a = e.seq_create(400)
+        lw, _ = e.prefill_logits([a], [prompts[0]], list(range(330)))
+        assert err(lw, refs[0]) < BF16_BAR
+        sids = [e.seq_create(400), e.seq_create(100)]
+        done = [0, 0]
+        for step in ([(0, 70), (1, 3)], [(0, 201), (1, 1)], [(0, 1), (1, 60)], [(0, 30), (1, 1)]):
+            chunks, rows, base = [], [], 0
+            for rq, c in step:
+                chunks.append(prompts[rq][done[rq]:done[rq] + c])
+                rows += list(range(base, base + c))
+                base += c
+            lg, _ = e.prefill_logits([sids[rq] for rq, _ in step], chunks, rows)
+            base = 0
+            for rq, c in step:
+                assert err(lg[base:base + c], refs[rq][done[rq]:done[rq] + c]) < BF16_BAR, "request %d at %d" % (rq, done[rq])
+                base += c
+                done[rq] += c
+        while done[1] < 75:
+            e.decode_step(sids, in_tokens=[prompts[0][done[0]], prompts[1][done[1]]], want_output=False)
+            lg = e.get_logits(2)
+            for rq in (0, 1):
+                assert err(lg[rq], refs[rq][done[rq]]) < BF16_BAR, "decoded request %d at %d" % (rq, done[rq])
+                done[rq] += 1
+    with engine(cfg, w) as e:     # the same model in fp32 keeps the plain layout everywhere
+        a = e.seq_create(100)
+        lw, _ = e.prefill_logits([a], [prompts[1]], list(range(75)))
+        assert err(lw, refs[1]) < F32_BAR
+
+
 @pytest.mark.parametrize("nseq", [3, 12, 27])
 def test_bf16_decode_batches_of_many_sizes(nseq):
     cfg = cfg_c()
