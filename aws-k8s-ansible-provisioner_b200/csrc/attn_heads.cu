@@ -171,13 +171,13 @@ __global__ void __launch_bounds__(128) heads_finish_kernel(const float* __restri
 }
 
 // Whole-row norms: q (all heads at once) and k (all key heads at once) are each divided by the root mean square of the row and
-// multiplied by a gain per entry; v passes.  One CTA per token.
-template <typename TC>
-__global__ void __launch_bounds__(128) heads_finish_rownorm_kernel(const float* __restrict__ proj, int ld, HeadsGeom g, const float* __restrict__ bias,
+// multiplied by a gain per entry; v passes.  One CTA of NT threads per token (wide CTAs for steps of few tokens).
+template <typename TC, int NT>
+__global__ void __launch_bounds__(NT) heads_finish_rownorm_kernel(const float* __restrict__ proj, int ld, HeadsGeom g, const float* __restrict__ bias,
                                                                    const float* __restrict__ qk_gain, const int32_t* __restrict__ slots,
                                                                    float* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache,
                                                                    bf16* __restrict__ q_bf16) {
-  __shared__ float red[2][4];
+  __shared__ float red[2][NT / 32];
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -186,11 +186,11 @@ __global__ void __launch_bounds__(128) heads_finish_rownorm_kernel(const float* 
   const int nq = g.heads * g.dim, nk = g.kv_heads * g.dim, nv = g.kv_heads * g.vdim;
   const float* row = proj + (size_t)t * ld;
   float sq = 0.f, sk = 0.f;
-  for (int i = threadIdx.x; i < nq; i += 128) {
+  for (int i = threadIdx.x; i < nq; i += NT) {
     const float v = row[i] + (bias ? bias[i] : 0.f);
     sq = fmaf(v, v, sq);
   }
-  for (int i = threadIdx.x; i < nk; i += 128) {
+  for (int i = threadIdx.x; i < nk; i += NT) {
     const float v = row[nq + i] + (bias ? bias[nq + i] : 0.f);
     sk = fmaf(v, v, sk);
   }
@@ -201,18 +201,24 @@ __global__ void __launch_bounds__(128) heads_finish_rownorm_kernel(const float* 
     red[1][warp] = sk;
   }
   __syncthreads();
-  const float rq = 1.0f / sqrtf((red[0][0] + red[0][1] + red[0][2] + red[0][3]) / (float)nq + g.eps);
-  const float rk = 1.0f / sqrtf((red[1][0] + red[1][1] + red[1][2] + red[1][3]) / (float)nk + g.eps);
+  float tq = 0.f, tk = 0.f;
+#pragma unroll
+  for (int w = 0; w < NT / 32; ++w) {
+    tq += red[0][w];
+    tk += red[1][w];
+  }
+  const float rq = 1.0f / sqrtf(tq / (float)nq + g.eps);
+  const float rk = 1.0f / sqrtf(tk / (float)nk + g.eps);
   if (g.swizzled) {   // the page layout of the GQA kernels (128-wide heads), queries as bf16
-    for (int i = threadIdx.x; i < nq; i += 128) q_bf16[(size_t)t * nq + i] = __float2bfloat16_rn((row[i] + (bias ? bias[i] : 0.f)) * rq * qk_gain[i]);
-    for (int i = threadIdx.x; i < nk; i += 128)
+    for (int i = threadIdx.x; i < nq; i += NT) q_bf16[(size_t)t * nq + i] = __float2bfloat16_rn((row[i] + (bias ? bias[i] : 0.f)) * rq * qk_gain[i]);
+    for (int i = threadIdx.x; i < nk; i += NT)
       stf(k_cache + swizzled_index(slot, i >> 7, g.kv_heads, i & 127), (row[nq + i] + (bias ? bias[nq + i] : 0.f)) * rk * qk_gain[nq + i]);
-    for (int i = threadIdx.x; i < nv; i += 128) stf(v_cache + swizzled_index(slot, i >> 7, g.kv_heads, i & 127), row[nq + nk + i] + (bias ? bias[nq + nk + i] : 0.f));
+    for (int i = threadIdx.x; i < nv; i += NT) stf(v_cache + swizzled_index(slot, i >> 7, g.kv_heads, i & 127), row[nq + nk + i] + (bias ? bias[nq + nk + i] : 0.f));
     return;
   }
-  for (int i = threadIdx.x; i < nq; i += 128) q_out[(size_t)t * nq + i] = (row[i] + (bias ? bias[i] : 0.f)) * rq * qk_gain[i];
-  for (int i = threadIdx.x; i < nk; i += 128) stf(k_cache + (size_t)slot * nk + i, (row[nq + i] + (bias ? bias[nq + i] : 0.f)) * rk * qk_gain[nq + i]);
-  for (int i = threadIdx.x; i < nv; i += 128) stf(v_cache + (size_t)slot * nv + i, row[nq + nk + i] + (bias ? bias[nq + nk + i] : 0.f));
+  for (int i = threadIdx.x; i < nq; i += NT) q_out[(size_t)t * nq + i] = (row[i] + (bias ? bias[i] : 0.f)) * rq * qk_gain[i];
+  for (int i = threadIdx.x; i < nk; i += NT) stf(k_cache + (size_t)slot * nk + i, (row[nq + i] + (bias ? bias[nq + i] : 0.f)) * rk * qk_gain[nq + i]);
+  for (int i = threadIdx.x; i < nv; i += NT) stf(v_cache + (size_t)slot * nv + i, row[nq + nk + i] + (bias ? bias[nq + nk + i] : 0.f));
 }
 
 __global__ void __launch_bounds__(128) conv_tail_store_kernel(const float* __restrict__ proj, int ld, int C, int taps,
@@ -781,12 +787,18 @@ int launch_heads_finish_rownorm(const float* proj, int ld, const HeadsGeom& g, c
   if (T <= 0) return 0;
   B2_REQUIRE(qk_gain != nullptr, "heads_finish_rownorm: the row norms need their gains");
   B2_REQUIRE(!g.swizzled || (!cache_f32 && g.dim == 128 && g.vdim == 128 && q_bf16 != nullptr), "heads_finish_rownorm: the swizzled page layout is bf16, 128 wide");
-  if (cache_f32)
-    B2_CUDA_OK(b2_launch(heads_finish_rownorm_kernel<float>, dim3(T), dim3(128), 0, s, proj, ld, g, bias, qk_gain, slots, q_out, (float*)k_cache, (float*)v_cache,
-                         (bf16*)nullptr));
-  else
-    B2_CUDA_OK(b2_launch(heads_finish_rownorm_kernel<bf16>, dim3(T), dim3(128), 0, s, proj, ld, g, bias, qk_gain, slots, q_out, (bf16*)k_cache, (bf16*)v_cache,
-                         (bf16*)q_bf16));
+  const bool wide = T < 1024 && g.heads * g.dim >= 1024;
+#define B2_ROWNORM(TC, NT, QB)                                                                                                                         \
+  B2_CUDA_OK(b2_launch(heads_finish_rownorm_kernel<TC, NT>, dim3(T), dim3(NT), 0, s, proj, ld, g, bias, qk_gain, slots, q_out, (TC*)k_cache, (TC*)v_cache, \
+                       (bf16*)(QB)))
+  if (cache_f32) {
+    if (wide) B2_ROWNORM(float, 512, nullptr);
+    else B2_ROWNORM(float, 128, nullptr);
+  } else {
+    if (wide) B2_ROWNORM(bf16, 512, q_bf16);
+    else B2_ROWNORM(bf16, 128, q_bf16);
+  }
+#undef B2_ROWNORM
   return 0;
 }
 

@@ -47,7 +47,7 @@ constexpr int LR_TOKENS = 8;
 __global__ void __launch_bounds__(256) lowrank_act_kernel(const float* __restrict__ lr, int ld, int lr_off, int rank, const float* __restrict__ w2,
                                                           const float* __restrict__ bias, const float* __restrict__ rate_log, float rate,
                                                           int per_head, int mode, float* __restrict__ out, int C, int T) {
-  extern __shared__ float lrs[];   // [LR_TOKENS][rank]
+  extern __shared__ __align__(16) float lrs[];   // [LR_TOKENS][rank]
   pdl_wait();
   pdl_launch_dependents();
   const int t0 = blockIdx.x * LR_TOKENS, tn = min(LR_TOKENS, T - t0);
@@ -67,9 +67,21 @@ __global__ void __launch_bounds__(256) lowrank_act_kernel(const float* __restric
     for (int tt = 0; tt < LR_TOKENS; ++tt) {
       if (tt < tn) {
         const float* l = lrs + tt * rank + r0;
+        if ((rank & 3) == 0) {     // sixteen bytes of the token's low-rank values at a time
 #pragma unroll
-        for (int x = 0; x < 16; ++x)
-          if (r0 + x < rank) z[tt] = fmaf(w[x], l[x], z[tt]);
+          for (int x = 0; x < 16; x += 4)
+            if (r0 + x < rank) {
+              const float4 lv = *reinterpret_cast<const float4*>(l + x);
+              z[tt] = fmaf(w[x], lv.x, z[tt]);
+              z[tt] = fmaf(w[x + 1], lv.y, z[tt]);
+              z[tt] = fmaf(w[x + 2], lv.z, z[tt]);
+              z[tt] = fmaf(w[x + 3], lv.w, z[tt]);
+            }
+        } else {
+#pragma unroll
+          for (int x = 0; x < 16; ++x)
+            if (r0 + x < rank) z[tt] = fmaf(w[x], l[x], z[tt]);
+        }
       }
     }
   }
@@ -91,7 +103,8 @@ __global__ void __launch_bounds__(256) lowrank_act_kernel(const float* __restric
 // thread convolves and activates channels of the CTA's range, then a warp per query / key head turns the head into a unit vector.
 // proj [T][ld] fp32 = q (kv_heads*dim) | k (kv_heads*dim) | v (heads*vdim) | beta logits (heads) | ...; out [T][C] = the finished q | k | v,
 // beta_out [T][heads].
-__global__ void __launch_bounds__(256) conv_unit_finish_kernel(const float* __restrict__ proj, int ld, StateGeom g, int taps,
+template <int TAPS>   // 0: any number of taps
+__global__ void __launch_bounds__(256) conv_unit_finish_kernel(const float* __restrict__ proj, int ld, StateGeom g, int taps_any,
                                                                const float* __restrict__ conv_w, const float* __restrict__ ring,
                                                                const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_first,
                                                                const int32_t* __restrict__ positions, const int32_t* __restrict__ slots,
@@ -100,6 +113,7 @@ __global__ void __launch_bounds__(256) conv_unit_finish_kernel(const float* __re
   pdl_launch_dependents();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (slots[t] < 0) return;
+  const int taps = TAPS > 0 ? TAPS : taps_any;
   const int pos = positions[t];
   const int nqk = g.kv_heads * g.dim, nv = g.heads * g.vdim, C = 2 * nqk + nv;
   const int units = 2 * g.kv_heads + g.heads, u_lo = blockIdx.y * upc, u_hi = min(units, u_lo + upc);
@@ -111,12 +125,24 @@ __global__ void __launch_bounds__(256) conv_unit_finish_kernel(const float* __re
   float* orow = out + (size_t)t * C;
   for (int c = c_lo + threadIdx.x; c < c_hi; c += 256) {
     float acc = 0.f;
-    for (int j = 0; j < taps; ++j) {          // y_t = sum_j w[c][j] * x_(t - taps + 1 + j), the last column is the current token's
-      const int d = taps - 1 - j;
-      float xx = 0.f;
-      if (d <= back) xx = (row - (size_t)d * ld)[c];
-      else if (pos - d >= 0) xx = rg[(size_t)((pos - d) % taps) * C + c];
-      acc = fmaf(conv_w[(size_t)c * taps + j], xx, acc);
+    if constexpr (TAPS > 0) {                 // every load of the channel in flight at once
+      float xx[TAPS], ww[TAPS];
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) {
+        const int d = TAPS - 1 - j;
+        ww[j] = conv_w[(size_t)c * TAPS + j];
+        xx[j] = d <= back ? (row - (size_t)d * ld)[c] : (pos - d >= 0 ? rg[(size_t)((pos - d) % TAPS) * C + c] : 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) acc = fmaf(ww[j], xx[j], acc);
+    } else {
+      for (int j = 0; j < taps; ++j) {        // y_t = sum_j w[c][j] * x_(t - taps + 1 + j), the last column is the current token's
+        const int d = taps - 1 - j;
+        float xx = 0.f;
+        if (d <= back) xx = (row - (size_t)d * ld)[c];
+        else if (pos - d >= 0) xx = rg[(size_t)((pos - d) % taps) * C + c];
+        acc = fmaf(conv_w[(size_t)c * taps + j], xx, acc);
+      }
     }
     orow[c] = silu_f(acc);
   }
@@ -408,8 +434,15 @@ int launch_conv_unit_finish(const float* proj, int ld, const StateGeom& g, int t
   B2_REQUIRE(taps >= 1 && conv_w && (ring || taps == 1) && row_seq && row_first && row_end, "conv_unit_finish: the convolution needs its weights and state");
   const int C = 2 * g.kv_heads * g.dim + g.heads * g.vdim;
   const int units = 2 * g.kv_heads + g.heads, upc = T >= 256 ? units : std::max(1, (units + 15) / 16);   // few tokens: up to sixteen CTAs each
-  B2_CUDA_OK(b2_launch(conv_unit_finish_kernel, dim3(T, (units + upc - 1) / upc), dim3(256), 0, s, proj, ld, g, taps, conv_w, (const float*)ring, row_seq,
-                       row_first, positions, slots, unit_eps, out, beta_out, upc));
+  const dim3 grid(T, (units + upc - 1) / upc);
+#define B2_CONV_FINISH(TAPS)                                                                                                                      \
+  B2_CUDA_OK(b2_launch(conv_unit_finish_kernel<TAPS>, grid, dim3(256), 0, s, proj, ld, g, taps, conv_w, (const float*)ring, row_seq, row_first, positions, \
+                       slots, unit_eps, out, beta_out, upc))
+  if (taps == 4) B2_CONV_FINISH(4);
+  else if (taps == 3) B2_CONV_FINISH(3);
+  else if (taps == 2) B2_CONV_FINISH(2);
+  else B2_CONV_FINISH(0);
+#undef B2_CONV_FINISH
   if (taps > 1)
     B2_CUDA_OK(b2_launch(conv_ring_store_kernel, dim3(T), dim3(128), 0, s, proj, ld, C, taps, ring, row_seq, row_end, positions, slots));
   return 0;

@@ -21,6 +21,19 @@ __device__ __forceinline__ float block_sum_128(float v, float* red) {
   return r;
 }
 
+// the same for a CTA of NT threads (NT a multiple of 32, at most 1024)
+template <int NT>
+__device__ __forceinline__ float block_sum_n(float v, float* red) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = 0.f;
+#pragma unroll
+  for (int w = 0; w < NT / 32; ++w) r += red[w];
+  __syncthreads();
+  return r;
+}
+
 template <typename TT>
 __global__ void __launch_bounds__(128) embed_unit_norm_kernel(const int32_t* __restrict__ ids, const TT* __restrict__ table,
                                                               const float* __restrict__ gain1p, float* __restrict__ h, int W, int vocab,
@@ -292,15 +305,16 @@ __global__ void __launch_bounds__(256) silu_gate_kernel(const float* __restrict_
   }
 }
 
-// h[t] += coef * (n(a) ga + n(b) gb) + d1 + sum_k y[slot_k]; then optionally x_next = n(h) * gain_next.  One CTA per row.
+// h[t] += coef * (n(a) ga + n(b) gb) + d1 + sum_k y[slot_k]; then optionally x_next = n(h) * gain_next.  One CTA of NT threads per row
+// (steps of few tokens take wide CTAs: a row is then two or three rounds of loads instead of sixteen).
 constexpr int BA_MAX_TOP = 16;
-template <typename TX>
-__global__ void __launch_bounds__(128) branch_add_kernel(float* __restrict__ h, const float* __restrict__ a, const float* __restrict__ gain_a,
-                                                         const float* __restrict__ b, const float* __restrict__ gain_b, float coef,
-                                                         const float* __restrict__ d1, const float* __restrict__ y,
-                                                         const int32_t* __restrict__ pair_slot, int top, int W, float eps,
-                                                         const float* __restrict__ gain_next, TX* __restrict__ x_next) {
-  __shared__ float red[4];
+template <typename TX, int NT>
+__global__ void __launch_bounds__(NT) branch_add_kernel(float* __restrict__ h, const float* __restrict__ a, const float* __restrict__ gain_a,
+                                                        const float* __restrict__ b, const float* __restrict__ gain_b, float coef,
+                                                        const float* __restrict__ d1, const float* __restrict__ y,
+                                                        const int32_t* __restrict__ pair_slot, int top, int W, float eps,
+                                                        const float* __restrict__ gain_next, TX* __restrict__ x_next) {
+  __shared__ float red[NT / 32];
   __shared__ int slot_s[BA_MAX_TOP];
   pdl_wait();
   pdl_launch_dependents();
@@ -311,19 +325,18 @@ __global__ void __launch_bounds__(128) branch_add_kernel(float* __restrict__ h, 
   float* hr = h + (size_t)t * W;
   if (y != nullptr && (int)threadIdx.x < min(top, BA_MAX_TOP)) slot_s[threadIdx.x] = pair_slot[(size_t)t * top + threadIdx.x];
   float ra = 1.0f, rb = 1.0f;
-  if (ar && gain_a) {
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < W; i += 128) ss = fmaf(ar[i], ar[i], ss);
-    ra = 1.0f / sqrtf(block_sum_128(ss, red) / (float)W + eps);
-  }
-  if (br && gain_b) {
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < W; i += 128) ss = fmaf(br[i], br[i], ss);
-    rb = 1.0f / sqrtf(block_sum_128(ss, red) / (float)W + eps);
+  {
+    float sa = 0.f, sb = 0.f;
+    if (ar && gain_a)
+      for (int i = threadIdx.x; i < W; i += NT) sa = fmaf(ar[i], ar[i], sa);
+    if (br && gain_b)
+      for (int i = threadIdx.x; i < W; i += NT) sb = fmaf(br[i], br[i], sb);
+    if (ar && gain_a) ra = 1.0f / sqrtf(block_sum_n<NT>(sa, red) / (float)W + eps);
+    if (br && gain_b) rb = 1.0f / sqrtf(block_sum_n<NT>(sb, red) / (float)W + eps);
   }
   __syncthreads();
   float ss2 = 0.f;
-  for (int i = threadIdx.x; i < W; i += 128) {
+  for (int i = threadIdx.x; i < W; i += NT) {
     float m = 0.f;
     if (ar) m = ar[i] * ra * (gain_a ? gain_a[i] : 1.0f);
     if (br) m += br[i] * rb * (gain_b ? gain_b[i] : 1.0f);
@@ -336,8 +349,8 @@ __global__ void __launch_bounds__(128) branch_add_kernel(float* __restrict__ h, 
     ss2 = fmaf(hn, hn, ss2);
   }
   if (gain_next != nullptr) {
-    const float r2 = 1.0f / sqrtf(block_sum_128(ss2, red) / (float)W + eps);
-    for (int i = threadIdx.x; i < W; i += 128) x_next[(size_t)t * W + i] = (TX)(hr[i] * r2 * gain_next[i]);   // its own writes
+    const float r2 = 1.0f / sqrtf(block_sum_n<NT>(ss2, red) / (float)W + eps);
+    for (int i = threadIdx.x; i < W; i += NT) x_next[(size_t)t * W + i] = (TX)(hr[i] * r2 * gain_next[i]);   // its own writes
   }
 }
 
@@ -448,10 +461,14 @@ int launch_branch_add(float* h, const float* a, const float* gain_a, const float
   if (T <= 0) return 0;
   B2_REQUIRE((gain_next == nullptr) == (x_next == nullptr), "branch_add: the following norm needs its gain and its output");
   B2_REQUIRE(y == nullptr || (pair_slot != nullptr && top >= 1), "branch_add: routed rows need their slots");
-  if (x_f32 || x_next == nullptr)
-    B2_CUDA_OK(b2_launch(branch_add_kernel<float>, dim3(T), dim3(128), 0, s, h, a, gain_a, b, gain_b, coef, d1, y, pair_slot, top, W, eps, gain_next, (float*)x_next));
-  else
-    B2_CUDA_OK(b2_launch(branch_add_kernel<bf16>, dim3(T), dim3(128), 0, s, h, a, gain_a, b, gain_b, coef, d1, y, pair_slot, top, W, eps, gain_next, (bf16*)x_next));
+  const bool wide = T < 1024 && W >= 1024;
+  if (x_f32 || x_next == nullptr) {
+    if (wide) B2_CUDA_OK(b2_launch(branch_add_kernel<float, 512>, dim3(T), dim3(512), 0, s, h, a, gain_a, b, gain_b, coef, d1, y, pair_slot, top, W, eps, gain_next, (float*)x_next));
+    else B2_CUDA_OK(b2_launch(branch_add_kernel<float, 128>, dim3(T), dim3(128), 0, s, h, a, gain_a, b, gain_b, coef, d1, y, pair_slot, top, W, eps, gain_next, (float*)x_next));
+  } else {
+    if (wide) B2_CUDA_OK(b2_launch(branch_add_kernel<bf16, 512>, dim3(T), dim3(512), 0, s, h, a, gain_a, b, gain_b, coef, d1, y, pair_slot, top, W, eps, gain_next, (bf16*)x_next));
+    else B2_CUDA_OK(b2_launch(branch_add_kernel<bf16, 128>, dim3(T), dim3(128), 0, s, h, a, gain_a, b, gain_b, coef, d1, y, pair_slot, top, W, eps, gain_next, (bf16*)x_next));
+  }
   return 0;
 }
 
