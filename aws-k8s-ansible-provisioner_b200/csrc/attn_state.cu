@@ -231,18 +231,26 @@ __global__ void __launch_bounds__(256) state_scan_kernel(const float* __restrict
   const int vcols = min(cols, g.vdim - col0);
   for (int i = threadIdx.x; i < 2 * CH * MAXC; i += nthreads) (&vs[0][0][0])[i] = 0.f;
   __syncthreads();
+  // (flat loops over a chunk's numbers keep every thread's copies in flight together; sizes that are powers of two -- the usual case --
+  // index by shifts instead of divisions)
+  const int dsh = (g.dim & (g.dim - 1)) == 0 ? 31 - __clz(g.dim) : -1, vsh = (vcols & (vcols - 1)) == 0 ? 31 - __clz(vcols) : -1;
+  const float* qb = q + (size_t)first * ldq + kh * g.dim;
+  const float* kb = k + (size_t)first * ldk + kh * g.dim;
+  const float* ab = decay + (size_t)first * ((size_t)g.heads * g.dim) + a * g.dim;
+  const float* vb = v + (size_t)first * ldv + a * g.vdim + col0;
+  const int lda = g.heads * g.dim;
   auto issue = [&](int c0, int st) {
     const int cn = min(CH, n - c0);
     for (int i = threadIdx.x; i < cn * g.dim; i += nthreads) {
-      const int tt = i / g.dim, d = i % g.dim, at = (d % SC_LANES) * LS + d / SC_LANES;
-      const size_t row = (size_t)(first + c0 + tt);
-      cp_async_f32(&qs[st][tt][at], q + row * ldq + kh * g.dim + d);
-      cp_async_f32(&ks[st][tt][at], k + row * ldk + kh * g.dim + d);
-      cp_async_f32(&as[st][tt][at], decay + row * ((size_t)g.heads * g.dim) + a * g.dim + d);
+      const int tt = dsh >= 0 ? i >> dsh : i / g.dim, d = dsh >= 0 ? i & (g.dim - 1) : i % g.dim, at = (d % SC_LANES) * LS + d / SC_LANES;
+      const int row = c0 + tt;
+      cp_async_f32(&qs[st][tt][at], qb + (size_t)row * ldq + d);
+      cp_async_f32(&ks[st][tt][at], kb + (size_t)row * ldk + d);
+      cp_async_f32(&as[st][tt][at], ab + (size_t)row * lda + d);
     }
     for (int i = threadIdx.x; i < cn * vcols; i += nthreads) {
-      const int tt = i / vcols, c = i % vcols;
-      cp_async_f32(&vs[st][tt][c], v + (size_t)(first + c0 + tt) * ldv + a * g.vdim + col0 + c);
+      const int tt = vsh >= 0 ? i >> vsh : i / vcols, c = vsh >= 0 ? i & (vcols - 1) : i % vcols;
+      cp_async_f32(&vs[st][tt][c], vb + (size_t)(c0 + tt) * ldv + c);
     }
     if (RULE == STATE_RULE_DELTA)
       for (int i = threadIdx.x; i < cn; i += nthreads) cp_async_f32(&bs[st][i], beta + (size_t)(first + c0 + i) * g.heads + a);
