@@ -1245,7 +1245,7 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
     }
     if (!have_norm) {
       KL k(e, B2K_NORM);
-      if (!k.skip()) B2_TRY(launch_group_norm(e->l_h, L.gain1, e->l_x1, f, T, W, 1, c.rms_eps, nullptr, st));
+      if (!k.skip()) B2_TRY(launch_unit_norm2(e->l_h, L.gain1, nullptr, e->l_x1, nullptr, f, T, W, c.rms_eps, nullptr, st));   // (a CTA per row; the gain as it is)
     }
     const bool has_ff = sp.ff != B2_FF_NONE;
     if (has_ff) B2_TRY(fork(e->l_ev[0], sF));      // the feed-forward needs the norm output only
@@ -1455,7 +1455,7 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
   }
   {
     KL k(e, B2K_NORM);
-    if (!k.skip()) B2_TRY(launch_group_norm(e->l_h, e->l_final_gain, e->l_xl, f, nlast, W, 1, c.rms_eps, ntiles > 0 ? e->d_last_rows : nullptr, st));
+    if (!k.skip()) B2_TRY(launch_unit_norm2(e->l_h, e->l_final_gain, nullptr, e->l_xl, nullptr, f, nlast, W, c.rms_eps, ntiles > 0 ? e->d_last_rows : nullptr, st));
   }
   {
     KL k(e, B2K_LMHEAD);
