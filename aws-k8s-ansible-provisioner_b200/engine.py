@@ -37,11 +37,11 @@ class EngineConfig:
     max_seqs: int = 64
     max_batch_tokens: int = 8192
     use_cuda_graphs: bool = True
-    arch: str = "qwen3"          # "qwen3" | "phi3" | "opt" (include/b2_engine.h, enum b2_arch)
+    arch: str = "qwen3"          # "qwen3" | "phi3" | "opt" | "lerasun" | "kedasun" | "bumalix" (include/b2_engine.h, enum b2_arch)
     rotary_dim: int = 0          # 0 = head_dim
     max_positions: int = 0       # OPT: learned position table rows - 2 (0 = max_model_len)
     sliding_window: int = 0      # Phi-3: attend to the last N keys only (0 = all)
-    layers: list | None = None   # layer-list families (arch "lerasun", "kedasun"): the "layers" entries of the model's config.json
+    layers: list | None = None   # layer-list families (arch "lerasun", "kedasun", "bumalix"): the "layers" entries of the model's config.json
     compute_f32: bool = False    # families with an fp32 path: operands, weights and cache in fp32
     logit_scale: float = 0.0     # lm_head output multiplier (0 = 1)
     embed_scale: float = 0.0     # embedding multiplier (0 = 1)
@@ -297,7 +297,8 @@ class Engine:
         return out
 
     def get_hidden_f32(self, layer: int, ntokens: int) -> np.ndarray:
-        """Residual stream after `layer` (-1 = the normed embeddings) of the last forward, families with an fp32 stream."""
+        """Residual stream after `layer` (-1 = the embedding output) of the last forward, families with an fp32 stream; with a looped run of
+        layers `layer` counts layer runs (a looped layer once per pass)."""
         out = np.zeros((ntokens, self.cfg.hidden), dtype=np.float32)
         check(self.lib.b2_get_hidden_f32(self.h, layer, ntokens, out.ctypes.data_as(C.POINTER(C.c_float))), self.lib)
         return out

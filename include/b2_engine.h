@@ -229,7 +229,8 @@ int  b2_get_logits(b2_engine* e, int32_t nseq, float* out_logits);
  * Only filled when debug capture was enabled with b2_set_debug(e, 1). */
 int  b2_set_debug(b2_engine* e, int32_t capture_hidden);
 int  b2_get_hidden(b2_engine* e, int32_t layer, int32_t ntokens, uint16_t* out_bf16);
-/* The same for families whose residual stream is fp32 (Lerasun): [ntokens][hidden] floats. */
+/* The same for families whose residual stream is fp32 (the layer-list families): [ntokens][hidden] floats.  In a model with a looped run of
+ * layers, `layer` counts layer RUNS (a looped layer once per pass, in the order they run); -1 is the embedding output. */
 int  b2_get_hidden_f32(b2_engine* e, int32_t layer, int32_t ntokens, float* out_f32);
 
 /* Measurement knobs that can change while the engine lives (bench.py's ablation leg, the two-lane tests); every
