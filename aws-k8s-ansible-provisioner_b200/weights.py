@@ -153,7 +153,7 @@ def kedasun_random_state_dict(model_cfg: dict, seed: int = 0) -> dict[str, torch
     return sd
 
 
-def bumalix_tensor_shapes(model_cfg: dict, rank_a: int = 16, rank_g: int = 24) -> dict[str, tuple[int, ...]]:
+def bumalix_tensor_shapes(model_cfg: dict, rank_a: int = 32, rank_g: int = 32) -> dict[str, tuple[int, ...]]:
     """Tensor names and shapes of a Bumalix checkpoint for the dict its config.json holds.  The widths of the low-rank first stages
     (a1, g1) are not in the config -- a checkpoint's tensors carry them -- so they are arguments here."""
     W, V = model_cfg["width"], model_cfg["vocab"]
@@ -193,7 +193,7 @@ def bumalix_tensor_shapes(model_cfg: dict, rank_a: int = 16, rank_g: int = 24) -
     return s
 
 
-def bumalix_random_state_dict(model_cfg: dict, seed: int = 0, rank_a: int = 16, rank_g: int = 24) -> dict[str, torch.Tensor]:
+def bumalix_random_state_dict(model_cfg: dict, seed: int = 0, rank_a: int = 32, rank_g: int = 32) -> dict[str, torch.Tensor]:
     """Random bf16 weights scaled by 1/sqrt(fan-in), gains around one, decays that forget over tens to hundreds of tokens."""
     g = torch.Generator().manual_seed(seed)
     sd = {}

@@ -280,7 +280,7 @@ def tensor_shapes(cfg: dict) -> dict:
             q = p + "mix.left."
             sh.update({q + "q": (H * D, W), q + "q.b": (H * D,), q + "k": (G * D, W), q + "k.b": (G * D,), q + "v": (G * Dv, W),
                        q + "v.b": (G * Dv,), q + "q.norm": (H * D,), q + "k.norm": (G * D,), q + "o": (W, H * Dv), q + "out": (W,)})
-            H, D, Dv, R = b["heads"], b["dim"], b["vdim"], b.get("rank", 16)
+            H, D, Dv, R = b["heads"], b["dim"], b["vdim"], b.get("rank", 4)
             q = p + "mix.right."
             sh.update({q + "q": (H * D, W), q + "k": (H * D, W), q + "v": (H * Dv, W), q + "g": (H * Dv, W), q + "o": (W, H * Dv),
                        q + "norm": (Dv,), q + "a1": (R, W), q + "a2": (H * D, R), q + "a2.b": (H * D,), q + "out": (W,)})
