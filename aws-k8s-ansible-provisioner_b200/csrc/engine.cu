@@ -335,8 +335,11 @@ struct b2_engine {
   void *l_loop_in = nullptr, *l_cat = nullptr, *l_av2 = nullptr;   // W_in [W][2W]; its input [x | x0]; the second mixer's gated read-out
   float *l_dec = nullptr, *l_beta = nullptr, *l_gate = nullptr, *l_so = nullptr, *l_mix2 = nullptr, *l_ffd = nullptr, *l_slot_scale = nullptr;
   size_t l_qd_cols = 0;
-  cudaStream_t l_side[2] = {nullptr, nullptr};   // short steps: the second mixer and the feed-forward of a layer run beside the first mixer
-  cudaEvent_t l_ev[4] = {nullptr, nullptr, nullptr, nullptr};
+  cudaStream_t l_side[3] = {nullptr, nullptr, nullptr};   // short steps: the second mixer (or the delta rule's low-rank stages), the feed-forward and the shared
+                                                          // expert of a layer run beside the first mixer
+  cudaEvent_t l_ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  float* l_upf2 = nullptr;           // the shared expert's gate | up sums and activation (its own, so that it can run beside the routed experts)
+  void* l_act2 = nullptr;
 };
 
 namespace {
@@ -1201,7 +1204,7 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
   // run on streams of their own beside the first mixer and meet again at the kernel that adds the branches into the stream (inside a
   // captured step these become parallel branches of the graph).  Profiled and debugged steps stay on one stream.
   const bool multi = T <= 256 && !e->profiling && !(e->debug_flags & 1) && e->skip_mask == 0 && e->l_side[0] != nullptr;
-  cudaStream_t sB = multi ? e->l_side[0] : st, sF = multi ? e->l_side[1] : st;
+  cudaStream_t sB = multi ? e->l_side[0] : st, sF = multi ? e->l_side[1] : st, sS = multi ? e->l_side[2] : st;
   auto fork = [&](cudaEvent_t ev, cudaStream_t to) -> int {     // `to` continues from this point of the main stream
     if (!multi) return 0;
     B2_CUDA_OK(cudaEventRecord(ev, st));
@@ -1249,6 +1252,8 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
     }
     const bool has_ff = sp.ff != B2_FF_NONE;
     if (has_ff) B2_TRY(fork(e->l_ev[0], sF));      // the feed-forward needs the norm output only
+    const bool shared_beside = sp.ff == B2_FF_SCALED_GATED_EXPERTS && sp.shared_ff > 0;
+    if (shared_beside) B2_TRY(fork(e->l_ev[4], sS));
     {
       KL k(e, B2K_GEMM_QKV);
       if (!k.skip()) B2_TRY(dense(e->l_x1, L.wqd, e->l_qd, T, L.nqd, W, st));
@@ -1306,20 +1311,25 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
     } else {
       const StateGeom sg{sp.heads, sp.kv_heads, sp.dim, sp.vdim, STATE_RULE_DELTA};
       const int nqk = sp.kv_heads * sp.dim, C = 2 * nqk + sp.heads * sp.vdim;
+      B2_TRY(fork(e->l_ev[1], sB));
+      first_on(sB);
+      {
+        KL k(e, B2K_ACT);   // decay exp(-exp(A_log) softplus(A2 (A1 n) + dt_bias)) and the output gate sigmoid(G2 (G1 n))
+        if (!k.skip()) {
+          B2_TRY(launch_lowrank_act(e->l_qd, L.nqd, L.n_fixed, L.rank_a, L.a2, L.a2_bias, LOWRANK_DECAY_SOFTPLUS, 0.f, L.a_log, sp.dim, e->l_dec, T,
+                                    sp.heads * sp.dim, sB));
+          B2_TRY(launch_lowrank_act(e->l_qd, L.nqd, L.n_fixed + L.rank_a, L.rank_g, L.g2, nullptr, LOWRANK_SIGMOID, 0.f, nullptr, 0, e->l_gate, T,
+                                    sp.heads * sp.vdim, sB));
+        }
+      }
+      if (multi) b2_pdl_skip_next();   // (the convolution's predecessor on the main stream is the projection, across the fork's record: keep it a full dependency)
       {
         KL k(e, B2K_ROPE_KV);
         if (!k.skip()) B2_TRY(launch_conv_unit_finish(e->l_qd, L.nqd, sg, sp.conv_taps, L.conv_w, R.ring, e->d_row_seq, e->d_row_first, e->d_row_end,
                                                       e->d_positions, e->d_slots, BUMALIX_UNIT_EPS, e->l_q, e->l_beta, T, st));
       }
-      {
-        KL k(e, B2K_ACT);   // decay exp(-exp(A_log) softplus(A2 (A1 n) + dt_bias)) and the output gate sigmoid(G2 (G1 n))
-        if (!k.skip()) {
-          B2_TRY(launch_lowrank_act(e->l_qd, L.nqd, L.n_fixed, L.rank_a, L.a2, L.a2_bias, LOWRANK_DECAY_SOFTPLUS, 0.f, L.a_log, sp.dim, e->l_dec, T,
-                                    sp.heads * sp.dim, st));
-          B2_TRY(launch_lowrank_act(e->l_qd, L.nqd, L.n_fixed + L.rank_a, L.rank_g, L.g2, nullptr, LOWRANK_SIGMOID, 0.f, nullptr, 0, e->l_gate, T,
-                                    sp.heads * sp.vdim, st));
-        }
-      }
+      B2_TRY(join(e->l_ev[2], sB));   // (the low-rank stages ran beside the convolution)
+      first_on(st);
       {
         KL k(e, B2K_CHAIN);
         if (!k.skip()) B2_TRY(launch_state_scan(e->l_q, C, e->l_q + nqk, C, e->l_q + 2 * nqk, C, e->l_dec, e->l_beta, sg, 1.0f, R.state, portions, last_rows,
@@ -1423,25 +1433,27 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
         }
       }
       yr = e->l_y;
-      if (sp.shared_ff > 0) {
+      if (sp.shared_ff > 0) {   // (buffers of its own: in short steps it runs beside the routed experts)
+        first_on(sS);
         {
           KL k(e, B2K_GEMM_GATEUP);
-          if (!k.skip()) B2_TRY(dense(e->l_x1, L.sh_up, e->l_upf, T, 2 * sp.shared_ff, W, sF));
+          if (!k.skip()) B2_TRY(dense(e->l_x1, L.sh_up, e->l_upf2, T, 2 * sp.shared_ff, W, sS));
         }
         {
           KL k(e, B2K_ACT);
-          if (!k.skip()) B2_TRY(launch_silu_gate(e->l_upf, nullptr, nullptr, e->l_act, f, T, sp.shared_ff, sF));
+          if (!k.skip()) B2_TRY(launch_silu_gate(e->l_upf2, nullptr, nullptr, e->l_act2, f, T, sp.shared_ff, sS));
         }
         {
           KL k(e, B2K_GEMM_DOWN);
-          if (!k.skip()) B2_TRY(dense(e->l_act, L.sh_down, e->l_ffd, T, W, sp.shared_ff, sF));
+          if (!k.skip()) B2_TRY(dense(e->l_act2, L.sh_down, e->l_ffd, T, W, sp.shared_ff, sS));
         }
         d1 = e->l_ffd;
       }
     }
     if (two) B2_TRY(join(e->l_ev[2], sB));
     if (has_ff) B2_TRY(join(e->l_ev[3], sF));
-    if (two || has_ff) first_on(st);
+    if (shared_beside) B2_TRY(join(e->l_ev[5], sS));
+    if (multi) b2_pdl_skip_next();
     {
       KL k(e, B2K_NORM);  // h += (mixer + ff); the next layer's norm output, unless the loop's input mix comes first
       const bool next_plain = r + 1 < e->runs.size() && !e->runs[r + 1].pass_start && e->skip_mask == 0;
@@ -2211,7 +2223,7 @@ int state_engine_alloc(b2_engine* e) {
   const bool looped = c.loop_times > 0 && c.loop_stop > c.loop_start;
   if (looped) B2_TRY(xalloc(&e->l_loop_in, W * 2 * W));
   e->ll.resize(c.num_layers);
-  size_t max_q = 1, max_dec = 1, max_hv = 1, max_hv2 = 1, max_heads = 1, max_up = 1, max_act = 1, gqa_scratch = 0;
+  size_t max_q = 1, max_dec = 1, max_hv = 1, max_hv2 = 1, max_heads = 1, max_up = 1, max_act = 1, max_sff = 0, gqa_scratch = 0;
   int max_top = 1, max_exp = 1;
   for (int l = 0; l < c.num_layers; ++l) {
     ListLayer& L = e->ll[l];
@@ -2287,8 +2299,9 @@ int state_engine_alloc(b2_engine* e) {
       }
       max_top = std::max(max_top, sp.top);
       max_exp = std::max(max_exp, sp.experts);
-      max_up = std::max({max_up, (size_t)sp.top * 2 * sp.ff_dim, (size_t)2 * sp.shared_ff});
-      max_act = std::max({max_act, (size_t)sp.top * sp.ff_dim, (size_t)sp.shared_ff});
+      max_up = std::max(max_up, (size_t)sp.top * 2 * sp.ff_dim);
+      max_act = std::max(max_act, (size_t)sp.top * sp.ff_dim);
+      max_sff = std::max(max_sff, (size_t)sp.shared_ff);
     } else {
       B2_REQUIRE(sp.ff == B2_FF_NONE, "layer %d: feed-forward kind %d not built for this family", l, sp.ff);
     }
@@ -2361,6 +2374,10 @@ int state_engine_alloc(b2_engine* e) {
   B2_TRY(aalloc(&e->l_av, Tc * max_hv));
   B2_TRY(aalloc(&e->l_av2, Tc * max_hv2));
   B2_TRY(aalloc(&e->l_act, Tc * max_act));
+  if (max_sff > 0) {
+    B2_TRY(dalloc(&e->l_upf2, Tc * 2 * max_sff));
+    B2_TRY(aalloc(&e->l_act2, Tc * max_sff));
+  }
   B2_TRY(aalloc(&e->l_xl, (size_t)e->l_rows_cap * W));
   B2_TRY(dalloc(&e->l_idx, Tc * max_top));
   e->l_offsets_stride = max_exp + 1;
@@ -3287,7 +3304,7 @@ extern "C" void b2_engine_free(b2_engine* e) {
     if (ev) cudaEventDestroy(ev);
   for (auto& sd : e->l_side)
     if (sd) cudaStreamDestroy(sd);
-  F(e->l_loop_in); F(e->l_cat); F(e->l_av2); F(e->l_dec); F(e->l_beta); F(e->l_gate); F(e->l_so); F(e->l_mix2); F(e->l_ffd); F(e->l_slot_scale);
+  F(e->l_upf2); F(e->l_act2); F(e->l_loop_in); F(e->l_cat); F(e->l_av2); F(e->l_dec); F(e->l_beta); F(e->l_gate); F(e->l_so); F(e->l_mix2); F(e->l_ffd); F(e->l_slot_scale);
   if (e->ev_fork) cudaEventDestroy(e->ev_fork);
   if (e->ev_join) cudaEventDestroy(e->ev_join);
   if (e->stream2) cudaStreamDestroy(e->stream2);

@@ -484,7 +484,7 @@ def family_models(pkg, weights, family, tag):
     if family == "bumalix":
         width, heads, inter = BUMALIX_SIZES[tag]
         mc = bumalix_model_cfg(width, heads, inter)
-        return [("bumalix", pkg.EngineConfig.bumalix(mc), lambda c: weights.bumalix_random_state_dict(mc, seed=0)),
+        return [("bumalix", pkg.EngineConfig.bumalix(mc), lambda c: weights.bumalix_random_state_dict(mc, seed=0, rank_a=16, rank_g=16)),   # (low-rank widths of 16)
                 ("qwen3", pkg.EngineConfig(num_layers=4, hidden=width, num_q_heads=heads, num_kv_heads=heads // 2, head_dim=128, intermediate=inter, vocab=32000),
                  lambda c: weights.random_state_dict(c, seed=0))]
     if family == "kedasun":
