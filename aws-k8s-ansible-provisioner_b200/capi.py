@@ -6,10 +6,11 @@ import os
 
 # B2_LIB_PATH: an alternative build of the same library (A/B measurements of one source change); never a fallback
 LIB_PATH = os.environ.get("B2_LIB_PATH") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "libb2engine.so")
-ABI_VERSION = 5
-ARCH_QWEN3, ARCH_PHI3, ARCH_OPT, ARCH_LERASUN, ARCH_KEDASUN, ARCH_BUMALIX = 0, 1, 2, 3, 4, 5
+ABI_VERSION = 6
+ARCH_QWEN3, ARCH_PHI3, ARCH_OPT, ARCH_LERASUN, ARCH_KEDASUN, ARCH_BUMALIX, ARCH_TINEVIK = 0, 1, 2, 3, 4, 5, 6
 MIXER_LATENT_ATTENTION, MIXER_ATTENTION, MIXER_CONV_ATTENTION, MIXER_WINDOW_AND_STATE, MIXER_DELTA_STATE = 1, 2, 3, 4, 5
-FF_NONE, FF_ROUTED_EXPERTS, FF_CLAMPED_GATED, FF_POLYNORM, FF_SCALED_GATED_EXPERTS = 0, 1, 2, 3, 4
+MIXER_DECAY_STATE, MIXER_MIXED_SCORE_ATTENTION, MIXER_GATED_LATENT = 6, 7, 8
+FF_NONE, FF_ROUTED_EXPERTS, FF_CLAMPED_GATED, FF_POLYNORM, FF_SCALED_GATED_EXPERTS, FF_XIELU, FF_TABLE_EXPERTS = 0, 1, 2, 3, 4, 5, 6
 NUM_KERNEL_CLASSES = 12
 
 
@@ -25,6 +26,8 @@ class b2_layer_spec(C.Structure):
         ("groups_keep", C.c_int32), ("kv_heads", C.c_int32), ("conv_taps", C.c_int32), ("window", C.c_int32),
         ("keep_first", C.c_int32), ("v_mix", C.c_int32), ("ff_limit", C.c_float),
         ("s_heads", C.c_int32), ("s_dim", C.c_int32), ("s_vdim", C.c_int32), ("s_tau", C.c_float), ("shared_ff", C.c_int32),
+        ("weights_of", C.c_int32), ("q_rank", C.c_int32), ("rot_factor", C.c_float), ("softcap", C.c_float), ("score_mix", C.c_int32),
+        ("rot_values", C.c_int32),
     ]
 
 
@@ -39,6 +42,7 @@ class b2_config(C.Structure):
         ("layer_specs", C.POINTER(b2_layer_spec)), ("compute_f32", C.c_int32), ("logit_scale", C.c_float),
         ("embed_scale", C.c_float), ("norm_groups", C.c_int32),
         ("loop_start", C.c_int32), ("loop_stop", C.c_int32), ("loop_times", C.c_int32), ("logit_softcap", C.c_float),
+        ("norm_kind", C.c_int32),
     ]
 
 
@@ -56,6 +60,7 @@ SIGNATURES = {
     "b2_abi_version": (_I, []),
     "b2_engine_create": (_I, [C.POINTER(b2_config), C.c_char_p, _I, C.POINTER(_P)]),
     "b2_engine_load_tensor": (_I, [_P, C.c_char_p, _P, C.c_size_t]),
+    "b2_engine_load_int_tensor": (_I, [_P, C.c_char_p, _I32P, C.c_size_t]),
     "b2_engine_load_safetensors": (_I, [_P, C.c_char_p]),
     "b2_engine_finalize": (_I, [_P]),
     "b2_engine_free": (None, [_P]),

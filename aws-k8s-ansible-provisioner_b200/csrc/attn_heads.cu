@@ -749,7 +749,287 @@ int launch_attention_t(const float* q, const void* k, const void* v, const Heads
                                                   seq_lens, (TO*)out, cross_cols);
 }
 
+// ---- mixers whose scores are mixed over the heads before the softmax ----
+// One CTA of 128 threads per token, a warp per head at a time (query heads, then key heads, then value heads).  The token's cosines and
+// sines are formed once: [rot_dims/2] for q and k (angles divided by rot_factor), [vdim/2] for the values.
+template <typename TC>
+__global__ void __launch_bounds__(128) heads_finish_halves_kernel(const float* __restrict__ proj, int ld, HeadsGeom g, const float* __restrict__ q_gain,
+                                                                  const float* __restrict__ k_gain, const int32_t* __restrict__ positions,
+                                                                  const int32_t* __restrict__ slots, float* __restrict__ q_out, TC* __restrict__ k_cache,
+                                                                  TC* __restrict__ v_cache) {
+  extern __shared__ float cs[];   // qk: cos [half] | sin [half]; then v: cos [vhalf] | sin [vhalf]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pos = positions[t], slot = slots[t];
+  const int half = g.rot_dims / 2, vhalf = g.rot_values ? g.vdim / 2 : 0;
+  float* vcs = cs + 2 * half;
+  const double inv_factor = g.rot_factor > 0.f ? 1.0 / (double)g.rot_factor : 1.0;
+  for (int i = threadIdx.x; i < half; i += 128) {
+    const double f = exp2(-2.0 * (double)i / (double)g.rot_dims * log2((double)g.rot_base)) * inv_factor;
+    double sd, cd;
+    sincos((double)pos * f, &sd, &cd);
+    cs[i] = (float)cd;
+    cs[half + i] = (float)sd;
+  }
+  for (int i = threadIdx.x; i < vhalf; i += 128) pair_cos_sin(pos, i, g.vdim, g.rot_base, &vcs[i], &vcs[vhalf + i]);
+  __syncthreads();
+  const float* row = proj + (size_t)t * ld;
+  const int nqk = g.heads + g.kv_heads;
+  for (int u = warp; u < nqk + g.kv_heads; u += 4) {
+    if (u < nqk) {
+      const bool is_q = u < g.heads;
+      const int a = is_q ? u : u - g.heads;
+      const float* src = row + (is_q ? a * g.dim : g.heads * g.dim + a * g.dim);
+      const float* gain = is_q ? q_gain : k_gain;
+      float r = 1.0f;
+      if (gain != nullptr) {
+        float ss = 0.f;
+        for (int d = lane; d < g.dim; d += 32) ss = fmaf(src[d], src[d], ss);
+        r = 1.0f / sqrtf(warp_sum(ss) / (float)g.dim + g.eps);
+      }
+      if (!is_q && slot < 0) continue;
+      float* qd = q_out + (size_t)t * g.heads * g.dim + (size_t)a * g.dim;
+      TC* kd = k_cache + ((size_t)(slot < 0 ? 0 : slot) * g.kv_heads + a) * g.dim;
+      for (int d = lane; d < g.dim; d += 32) {
+        float y = gain != nullptr ? src[d] * r * gain[d] : src[d];
+        if (d < g.rot_dims) {
+          const int i = d < half ? d : d - half, o = d < half ? d + half : d - half;
+          const float z = gain != nullptr ? src[o] * r * gain[o] : src[o];
+          y = d < half ? y * cs[i] - z * cs[half + i] : y * cs[i] + z * cs[half + i];
+        }
+        if (is_q) qd[d] = y;
+        else stf(kd + d, y);
+      }
+    } else {
+      if (slot < 0) continue;
+      const int a = u - nqk;
+      const float* src = row + (g.heads + g.kv_heads) * g.dim + a * g.vdim;
+      TC* vd = v_cache + ((size_t)slot * g.kv_heads + a) * g.vdim;
+      for (int d = lane; d < g.vdim; d += 32) {
+        float y = src[d];
+        if (d < 2 * vhalf) {
+          const int i = d < vhalf ? d : d - vhalf;
+          const float z = src[d < vhalf ? d + vhalf : d - vhalf];
+          y = d < vhalf ? y * vcs[i] - z * vcs[vhalf + i] : y * vcs[i] + z * vcs[vhalf + i];
+        }
+        stf(vd + d, y);
+      }
+    }
+  }
+}
+
+// All heads of `qt` query tokens of one sequence per CTA (eight warps), because a mixed score of one head needs the scores of every head
+// for the same (query, key) pair.  Keys go by in tiles of 32, upwards from the first visible one.  Per tile: for every key/value head its
+// K rows are staged and the group's query heads score them (lane j scores key j; scale, cap); then every (token, head) mixes its row of
+// scores over the heads, masks it and updates its running maximum, sum and weights; then for every key/value head its V rows are staged
+// and the group's heads accumulate (lane c holds value columns c, c + 32, ...; the running sums live in shared memory).  The end divides,
+// turns the sum back by the query's position when the values were rotated, and rounds to the output type.
+constexpr int PM_WARPS = 8, PM_KEYS = 32;
+struct PremixArgs {
+  const float* q;
+  const void* k_cache;
+  const void* v_cache;
+  HeadsGeom g;
+  const float* mix;
+  const int32_t* block_table;
+  int bt_stride, block_size;
+  const PrefillTile* tiles;
+  const int32_t* positions;
+  const int32_t* seq_lens;
+  void* out;
+  int qt;
+};
+__host__ __device__ inline int premix_kv_stride(const HeadsGeom& g) { return (g.dim > g.vdim ? g.dim : g.vdim) | 1; }
+__host__ __device__ inline size_t premix_smem_floats(const HeadsGeom& g, int qt) {
+  return (size_t)qt * g.heads * (g.dim + g.vdim + 2 * PM_KEYS + 3) + (size_t)PM_KEYS * premix_kv_stride(g) + (size_t)g.heads * g.heads;
+}
+
+template <typename TC, typename TX>
+__global__ void __launch_bounds__(PM_WARPS * 32) heads_attention_premix_kernel(PremixArgs a) {
+  extern __shared__ float sm[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const HeadsGeom& g = a.g;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int H = g.heads, G = g.kv_heads, rep = H / G, D = g.dim, V = g.vdim, SD = premix_kv_stride(g);
+  int q_row0, q_pos0, nrows, bt_row;
+  if (a.tiles != nullptr) {
+    const PrefillTile tl = a.tiles[blockIdx.x];
+    q_row0 = tl.q_row0; q_pos0 = tl.q_pos0; nrows = tl.nrows; bt_row = tl.bt_row;
+  } else {
+    q_row0 = blockIdx.x; q_pos0 = a.positions[blockIdx.x]; nrows = a.seq_lens[blockIdx.x] > 0 ? 1 : 0; bt_row = blockIdx.x;
+  }
+  const int tok0 = blockIdx.y * a.qt;
+  const int ntok = min(a.qt, nrows - tok0);
+  TX* out = reinterpret_cast<TX*>(a.out);
+  if (ntok <= 0) {
+    if (a.tiles == nullptr && blockIdx.y == 0)   // an empty row of a padded decode batch: zeros
+      for (int i = threadIdx.x; i < H * V; i += PM_WARPS * 32) stf(out + (size_t)q_row0 * H * V + i, 0.f);
+    return;
+  }
+  float* Qs = sm;                                  // [qt][H][D]
+  float* Os = Qs + (size_t)a.qt * H * D;           // [qt][H][V]
+  float* Ss = Os + (size_t)a.qt * H * V;           // [qt][H][32] capped scores
+  float* Ps = Ss + (size_t)a.qt * H * PM_KEYS;     // [qt][H][32] weights
+  float* Ms = Ps + (size_t)a.qt * H * PM_KEYS;     // [qt][H] running maximum
+  float* Ls = Ms + (size_t)a.qt * H;               // [qt][H] running sum
+  float* Cs = Ls + (size_t)a.qt * H;               // [qt][H] this tile's rescale factor
+  float* KV = Cs + (size_t)a.qt * H;               // [32][SD]
+  float* Tk = KV + (size_t)PM_KEYS * SD;           // [H][H]
+  const int pos_lo = q_pos0 + tok0, pos_hi = pos_lo + ntok - 1;
+  const int items = ntok * H;
+  {
+    const float* qsrc = a.q + (size_t)(q_row0 + tok0) * H * D;
+    for (int i = threadIdx.x; i < items * D; i += PM_WARPS * 32) Qs[i] = qsrc[i];
+    for (int i = threadIdx.x; i < items * V; i += PM_WARPS * 32) Os[i] = 0.f;
+    for (int i = threadIdx.x; i < items; i += PM_WARPS * 32) {
+      Ms[i] = -INFINITY;
+      Ls[i] = 0.f;
+    }
+    if (a.mix != nullptr)
+      for (int i = threadIdx.x; i < H * H; i += PM_WARPS * 32) Tk[i] = a.mix[i];
+  }
+  const TC* kc = reinterpret_cast<const TC*>(a.k_cache);
+  const TC* vc = reinterpret_cast<const TC*>(a.v_cache);
+  const int32_t* bt = a.block_table + (size_t)bt_row * a.bt_stride;
+  const int k_first = g.window > 0 ? max(0, pos_lo - g.window + 1) / PM_KEYS * PM_KEYS : 0;
+  for (int k0 = k_first; k0 <= pos_hi; k0 += PM_KEYS) {
+    const int nk = min(PM_KEYS, pos_hi + 1 - k0);
+    for (int kvh = 0; kvh < G; ++kvh) {
+      __syncthreads();   // the staged rows' last readers are done (first time: Qs is in place)
+      for (int j = warp; j < nk; j += PM_WARPS) {
+        const int kp = k0 + j;
+        const TC* src = kc + (((size_t)bt[kp / a.block_size] * a.block_size + kp % a.block_size) * G + kvh) * D;
+        for (int d = lane; d < D; d += 32) KV[j * SD + d] = ldf(src + d);
+      }
+      __syncthreads();
+      for (int it = warp; it < ntok * rep; it += PM_WARPS) {
+        const int tok = it / rep, h = kvh * rep + (it - tok * rep);
+        if (lane < nk) {
+          const float* qv = Qs + ((size_t)tok * H + h) * D;
+          const float* kr = KV + lane * SD;
+          float acc = 0.f;
+          for (int d = 0; d < D; ++d) acc = fmaf(qv[d], kr[d], acc);
+          acc *= g.scale;
+          if (g.softcap > 0.f) acc = g.softcap * tanhf(acc / g.softcap);
+          Ss[((size_t)tok * H + h) * PM_KEYS + lane] = acc;
+        }
+      }
+    }
+    __syncthreads();
+    for (int it = warp; it < items; it += PM_WARPS) {
+      const int tok = it / H, h = it - tok * H;
+      const int my_pos = pos_lo + tok, kp = k0 + lane;
+      const bool vis = lane < nk && kp <= my_pos && (g.window <= 0 || my_pos - kp < g.window);
+      float sc = -INFINITY;
+      if (vis) {
+        if (a.mix != nullptr) {
+          sc = 0.f;
+          for (int b = 0; b < H; ++b) sc = fmaf(Tk[h * H + b], Ss[((size_t)tok * H + b) * PM_KEYS + lane], sc);
+        } else {
+          sc = Ss[(size_t)it * PM_KEYS + lane];
+        }
+      }
+      const float m_old = Ms[it];
+      const float m_new = fmaxf(m_old, warp_max(sc));
+      const float p = vis ? expf(sc - m_new) : 0.f;
+      const float corr = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+      const float psum = warp_sum(p);
+      Ps[(size_t)it * PM_KEYS + lane] = p;
+      if (lane == 0) {
+        Ms[it] = m_new;
+        Ls[it] = Ls[it] * corr + psum;
+        Cs[it] = corr;
+      }
+    }
+    for (int kvh = 0; kvh < G; ++kvh) {
+      __syncthreads();   // the weights are written / the staged rows' last readers are done
+      for (int j = warp; j < nk; j += PM_WARPS) {
+        const int kp = k0 + j;
+        const TC* src = vc + (((size_t)bt[kp / a.block_size] * a.block_size + kp % a.block_size) * G + kvh) * V;
+        for (int d = lane; d < V; d += 32) KV[j * SD + d] = ldf(src + d);
+      }
+      __syncthreads();
+      for (int it = warp; it < ntok * rep; it += PM_WARPS) {
+        const int tok = it / rep, h = kvh * rep + (it - tok * rep);
+        const size_t row = (size_t)tok * H + h;
+        const float corr = Cs[row];
+        const float* pw = Ps + row * PM_KEYS;
+        for (int d = lane; d < V; d += 32) {
+          float acc = Os[row * V + d] * corr;
+          for (int j = 0; j < nk; ++j) acc = fmaf(pw[j], KV[j * SD + d], acc);
+          Os[row * V + d] = acc;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int vhalf = g.rot_values ? V / 2 : 0;
+  for (int it = warp; it < items; it += PM_WARPS) {
+    const int tok = it / H;
+    const float inv = 1.0f / Ls[it];
+    const float* o = Os + (size_t)it * V;
+    TX* dst = out + (size_t)(q_row0 + tok0) * H * V + (size_t)it * V;
+    for (int d = lane; d < V; d += 32) {
+      float y = o[d];
+      if (d < 2 * vhalf) {   // turned back by the query's position: the pair (u, v) by minus the angle
+        const int i = d < vhalf ? d : d - vhalf;
+        float c, sn;
+        pair_cos_sin(pos_lo + tok, i, V, g.rot_base, &c, &sn);
+        const float z = o[d < vhalf ? d + vhalf : d - vhalf];
+        y = d < vhalf ? y * c + z * sn : y * c - z * sn;
+      }
+      stf(dst + d, y * inv);
+    }
+  }
+}
+
+template <typename TC, typename TX>
+int launch_premix_t(const PremixArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
+  static B2PerDeviceOnce once;
+  static size_t set_to = 0;
+  if (smem > 48 * 1024 && (once.need() || smem > set_to)) {
+    B2_CUDA_OK(cudaFuncSetAttribute(heads_attention_premix_kernel<TC, TX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max(smem, set_to)));
+    set_to = std::max(smem, set_to);
+  }
+  B2_CUDA_OK(b2_launch(heads_attention_premix_kernel<TC, TX>, grid, dim3(PM_WARPS * 32), smem, s, a));
+  return 0;
+}
+
 }  // namespace
+
+int launch_heads_finish_halves(const float* proj, int ld, const HeadsGeom& g, const float* q_gain, const float* k_gain, const int32_t* positions,
+                               const int32_t* slots, float* q_out, void* k_cache, void* v_cache, int cache_f32, int T, cudaStream_t s) {
+  if (T <= 0) return 0;
+  B2_REQUIRE(g.rot_dims >= 0 && g.rot_dims <= g.dim && g.rot_dims % 2 == 0, "heads_finish_halves: rot dims %d must be even and <= dim %d", g.rot_dims, g.dim);
+  B2_REQUIRE(!g.rot_values || g.vdim % 2 == 0, "heads_finish_halves: rotated values need an even vdim (%d)", g.vdim);
+  const size_t smem = (size_t)(g.rot_dims + (g.rot_values ? g.vdim : 0) + 2) * sizeof(float);
+  if (cache_f32)
+    B2_CUDA_OK(b2_launch(heads_finish_halves_kernel<float>, dim3(T), dim3(128), smem, s, proj, ld, g, q_gain, k_gain, positions, slots, q_out,
+                         (float*)k_cache, (float*)v_cache));
+  else
+    B2_CUDA_OK(b2_launch(heads_finish_halves_kernel<bf16>, dim3(T), dim3(128), smem, s, proj, ld, g, q_gain, k_gain, positions, slots, q_out,
+                         (bf16*)k_cache, (bf16*)v_cache));
+  return 0;
+}
+
+int launch_heads_attention_premix(const float* q, const void* k_cache, const void* v_cache, int cache_f32, const HeadsGeom& g, const float* mix,
+                                  const int32_t* block_table, int bt_stride, int block_size, const PrefillTile* tiles, int ntiles,
+                                  const int32_t* positions, const int32_t* seq_lens, void* out, int out_f32, int T, cudaStream_t s) {
+  if (T <= 0 || (tiles != nullptr && ntiles <= 0)) return 0;
+  B2_REQUIRE(g.heads >= 1 && g.kv_heads >= 1 && g.heads % g.kv_heads == 0, "heads_attention_premix: %d heads over %d key/value heads", g.heads, g.kv_heads);
+  B2_REQUIRE(cache_f32 == out_f32, "heads_attention_premix: cache and output have one element type");
+  // query tokens per CTA: as many as fit beside a second CTA on the SM, at least one
+  int qt = tiles != nullptr ? 16 : 1;
+  while (qt > 1 && premix_smem_floats(g, qt) * 4 > 100 * 1024) qt >>= 1;
+  const size_t smem = premix_smem_floats(g, qt) * sizeof(float);
+  B2_REQUIRE(smem <= 200 * 1024, "heads_attention_premix: %d heads of %d + %d numbers need %zu bytes of shared memory for one token", g.heads, g.dim, g.vdim, smem);
+  PremixArgs a{q, k_cache, v_cache, g, mix, block_table, bt_stride, block_size, tiles, positions, seq_lens, out, qt};
+  const dim3 grid(tiles != nullptr ? ntiles : T, tiles != nullptr ? (64 + qt - 1) / qt : 1);
+  if (cache_f32) return launch_premix_t<float, float>(a, grid, smem, s);
+  return launch_premix_t<bf16, bf16>(a, grid, smem, s);
+}
 
 int launch_heads_finish(const float* proj, int ld, const HeadsGeom& g, const float* bias, const float* conv_w, float* ring,
                         const int32_t* row_seq, const int32_t* row_first, const int32_t* row_end, const int32_t* positions,

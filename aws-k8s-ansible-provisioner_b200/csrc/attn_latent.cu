@@ -122,6 +122,37 @@ __global__ void __launch_bounds__(128) latent_finish_kernel(const float* __restr
   }
 }
 
+// What follows a fused projection whose output holds a query latent and a key/value latent (proj [T][ld] fp32, the query latent of
+// q_rank entries at column off_q, the other of kv_rank entries at off_c): both are RMS-normed with a plain gain; the first goes out as the
+// operand of the query up-projection, the second is the token's cache row.  One CTA of 128 threads per token.
+template <typename TX, typename TC>
+__global__ void __launch_bounds__(128) latent_pair_finish_kernel(const float* __restrict__ proj, int ld, int off_q, int q_rank, int off_c, int kv_rank,
+                                                                 const float* __restrict__ gain_q, const float* __restrict__ gain_c, float eps,
+                                                                 const int32_t* __restrict__ slots, TX* __restrict__ xq, TC* __restrict__ cache) {
+  __shared__ float red[2][4];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const float* row = proj + (size_t)t * ld;
+  float sq = 0.f, sc = 0.f;
+  for (int i = threadIdx.x; i < q_rank; i += 128) sq = fmaf(row[off_q + i], row[off_q + i], sq);
+  for (int i = threadIdx.x; i < kv_rank; i += 128) sc = fmaf(row[off_c + i], row[off_c + i], sc);
+  sq = warp_sum(sq);
+  sc = warp_sum(sc);
+  if ((threadIdx.x & 31) == 0) {
+    red[0][threadIdx.x >> 5] = sq;
+    red[1][threadIdx.x >> 5] = sc;
+  }
+  __syncthreads();
+  const float rq = 1.0f / sqrtf((red[0][0] + red[0][1] + red[0][2] + red[0][3]) / (float)q_rank + eps);
+  const float rc = 1.0f / sqrtf((red[1][0] + red[1][1] + red[1][2] + red[1][3]) / (float)kv_rank + eps);
+  for (int i = threadIdx.x; i < q_rank; i += 128) stf(xq + (size_t)t * q_rank + i, row[off_q + i] * rq * gain_q[i]);
+  const int slot = slots[t];
+  if (slot < 0) return;
+  TC* crow = cache + (size_t)slot * kv_rank;
+  for (int i = threadIdx.x; i < kv_rank; i += 128) stf(crow + i, row[off_c + i] * rc * gain_c[i]);
+}
+
 constexpr int LA_WARPS = 8, LA_KEYS = 32;
 
 // NR = ceil(kv_rank / 32): latent dims per lane
@@ -166,7 +197,9 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(const f
   for (int i = 0; i < NR; ++i) o[i] = 0.f;
   float m = -INFINITY, l = 0.f;
   const int32_t* bt = block_table + (size_t)bt_row * bt_stride;
-  for (int k0 = 0; k0 <= max_pos; k0 += LA_KEYS) {
+  // with a window the keys below the first row's window are hidden from every row of the CTA
+  const int k_first = g.window > 0 ? max(0, q_pos0 + first / g.heads - g.window + 1) / LA_KEYS * LA_KEYS : 0;
+  for (int k0 = k_first; k0 <= max_pos; k0 += LA_KEYS) {
     __syncthreads();  // previous tile consumed (and, first time, q staged)
     const int nk = min(LA_KEYS, max_pos + 1 - k0);
     for (int j = warp; j < nk; j += LA_WARPS) {
@@ -178,7 +211,7 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(const f
     if (!active || k0 > my_pos) continue;
     // lane j scores key k0 + j
     float s = -INFINITY;
-    if (lane < nk && k0 + lane <= my_pos) {
+    if (lane < nk && k0 + lane <= my_pos && (g.window <= 0 || my_pos - (k0 + lane) < g.window)) {
       const float* kr = ks + lane * SD;
       const float* q = qs + warp * D;
       float acc = 0.f;
@@ -204,8 +237,8 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(const f
     }
   }
   if (!active) return;
-  // the sink: one more term of the denominator
-  const float sk = sink[head];
+  // the sink: one more term of the denominator (none: its weight is zero)
+  const float sk = sink != nullptr ? sink[head] : -INFINITY;
   const float mf = fmaxf(m, sk);
   const float corr = expf(m - mf);
   const float den = l * corr + expf(sk - mf);
@@ -272,8 +305,10 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
   const int max_pos = q_pos0 + last_row / g.heads;
   // this split's keys: whole 64-key tiles [t_lo, t_hi)
   const int ntile = max_pos / MA_KEYS + 1;
-  const int per = (ntile + a.nsplit - 1) / a.nsplit;
-  const int t_lo = split * per, t_hi = min(ntile, t_lo + per);
+  // with a window the tiles below the first row's window are hidden from every row of the block
+  const int t_first = g.window > 0 ? max(0, q_pos0 + first / g.heads - g.window + 1) / MA_KEYS : 0;
+  const int per = (ntile - t_first + a.nsplit - 1) / a.nsplit;
+  const int t_lo = t_first + split * per, t_hi = min(ntile, t_lo + per);
 
   // ---- stage Q (bf16), zero the padding columns of both operand slabs ----
   if (R % 4 == 0 && g.rot_dim % 4 == 0) {   // one flat loop over (row, four floats): many independent loads per thread
@@ -422,10 +457,11 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
     const int k0 = t * MA_KEYS;
     load_keys(k0);
     scores();
-    const int lim = row_pos[r4] - k0;  // keys j <= lim are visible
+    const int lim = row_pos[r4] - k0;  // keys j <= lim are visible ...
+    const int low = g.window > 0 ? lim - g.window + 1 : -(1 << 30);   // ... from j = low on
     float tmax = -INFINITY;
     for (int j = q4 * 16; j < q4 * 16 + 16; ++j)
-      if (j <= lim) tmax = fmaxf(tmax, Ss[r4 * 68 + j] * g.scale);
+      if (j <= lim && j >= low) tmax = fmaxf(tmax, Ss[r4 * 68 + j] * g.scale);
     tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
     tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
     const bool move = tmax > m_ref + REF_SLACK || (m_ref == -INFINITY && tmax > -INFINITY);
@@ -450,7 +486,7 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
     }
     for (int j = q4 * 16; j < q4 * 16 + 16; ++j) {
       float p = 0.f;
-      if (j <= lim) p = expf(Ss[r4 * 68 + j] * g.scale - m_ref);
+      if (j <= lim && j >= low) p = expf(Ss[r4 * 68 + j] * g.scale - m_ref);
       const bf16 pb = __float2bfloat16_rn(p);
       Ps[r4 * 72 + j] = pb;
       mysum += __bfloat162float(pb);   // the weights that are summed are the weights that multiply the latents
@@ -494,7 +530,7 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
     const size_t base = (size_t)(q_row0 + tok) * g.heads + head;
     const float m = row_m[r], l = row_l[r];
     if (a.nsplit == 1) {
-      const float sk = a.sink[head];
+      const float sk = a.sink != nullptr ? a.sink[head] : -INFINITY;
       const float mf = fmaxf(m, sk);
       const float corr = m == -INFINITY ? 0.f : expf(m - mf);
       const float inv = corr / (l * corr + expf(sk - mf));
@@ -523,7 +559,7 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restri
   if (seq_lens != nullptr && seq_lens[tok] <= 0) return;
   const float* p = partial + (size_t)row * nsplit * (R + 2);
   if (threadIdx.x < 32) {   // lane s holds split s (nsplit <= 32): its maximum, then its weight exp(m_s - m)
-    const float sk = sink[head];
+    const float sk = sink != nullptr ? sink[head] : -INFINITY;
     const float m = lane < nsplit ? p[(size_t)lane * (R + 2)] : -INFINITY;
     const float l = lane < nsplit ? p[(size_t)lane * (R + 2) + 1] : 0.f;
     const float mf = fmaxf(warp_max(m), sk);
@@ -609,6 +645,18 @@ int launch_latent_finish(const float* qd, int ld, const LatentGeom& g, int has_k
   else
     B2_CUDA_OK(b2_launch(latent_finish_kernel<bf16, bf16>, dim3(T), dim3(128), smem, s, qd, ld, g, has_kv, latent_gain, positions, slots,
                          (bf16*)q_nope, q_rot, (bf16*)cache));
+  return 0;
+}
+
+int launch_latent_pair_finish(const float* proj, int ld, int off_q, int q_rank, int off_c, int kv_rank, const float* gain_q, const float* gain_c,
+                              float eps, const int32_t* slots, void* xq, void* cache, int x_f32, int T, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (x_f32)
+    B2_CUDA_OK(b2_launch(latent_pair_finish_kernel<float, float>, dim3(T), dim3(128), 0, s, proj, ld, off_q, q_rank, off_c, kv_rank, gain_q, gain_c, eps,
+                         slots, (float*)xq, (float*)cache));
+  else
+    B2_CUDA_OK(b2_launch(latent_pair_finish_kernel<bf16, bf16>, dim3(T), dim3(128), 0, s, proj, ld, off_q, q_rank, off_c, kv_rank, gain_q, gain_c, eps,
+                         slots, (bf16*)xq, (bf16*)cache));
   return 0;
 }
 

@@ -106,6 +106,14 @@ struct ListLayer {
         *out_gain_r = nullptr, *poly = nullptr;
   size_t a2_floats = 0, g2_floats = 0;
   std::vector<uint16_t> a1_host, g1_host;
+  // Layer norms with gain and bias around every sublayer (Tinevik): gain1 / gain1b / gain2 / gain2b hold the gains, these the biases.  Its
+  // state mixer projects q | k | v | g (| a1) in `wqd` (off_s*), its softmax mixer q | k | v with one gain per head entry for q and for k
+  // (`qk_gain` = [dim] | [dim]) and the score-mixing matrix `talk`, its latent mixer dq | dkv | g in `wqd` (off_sq / off_sk / off_sg), the
+  // query up-projection `uq` and the two latent gains (`latq_gain`, `lat_gain`).  `poly` holds the dense activation's two numbers, `table`
+  // the experts of every token id [vocab][top].
+  float *bias1 = nullptr, *bias1b = nullptr, *bias2 = nullptr, *bias2b = nullptr, *latq_gain = nullptr;
+  void* uq = nullptr;
+  int32_t* table = nullptr;
 };
 // One run of a layer.  A looped layer runs once per pass with the same weights (ListLayer) but a cache and state of its own.
 struct ListRun {
@@ -115,7 +123,7 @@ struct ListRun {
   float* state = nullptr;      // [sequence slots][2][heads][dim][vdim] fp32 (attn_state.cu)
   float* ring = nullptr;       // [sequence slots][taps][channels] fp32: the convolutions' last inputs
 };
-inline bool list_arch(int arch) { return arch == B2_ARCH_LERASUN || arch == B2_ARCH_KEDASUN || arch == B2_ARCH_BUMALIX; }
+inline bool list_arch(int arch) { return arch == B2_ARCH_LERASUN || arch == B2_ARCH_KEDASUN || arch == B2_ARCH_BUMALIX || arch == B2_ARCH_TINEVIK; }
 
 struct Seq {
   bool active = false;
@@ -308,7 +316,7 @@ struct b2_engine {
   size_t esz = 2;              // bytes per operand element
   int v_pad = 0;               // row stride of the bf16 logits the sampler reads (vocab rounded up to 8)
   void *l_embed = nullptr, *l_head = nullptr;
-  float *l_embed_gain = nullptr, *l_final_gain = nullptr;
+  float *l_embed_gain = nullptr, *l_final_gain = nullptr, *l_final_bias = nullptr;
   char* l_pool = nullptr;      // the latent cache
   float *l_h = nullptr, *l_qd = nullptr, *l_qrot = nullptr, *l_qabs = nullptr, *l_mix = nullptr, *l_y = nullptr, *l_rw = nullptr,
         *l_logits = nullptr;
@@ -1484,6 +1492,246 @@ int forward_state_list(b2_engine* e, int T, int ntiles, int nlast) {
   return 0;
 }
 
+// Tinevik: h <- h + ln1b(mixer(ln1(h))), then h <- h + ln2b(ff(ln2(h))) on the same fp32 residual stream, every norm a layer norm with gain
+// and bias.  The layers run in the order of e->runs; a run names the layer whose tensors it uses (a layer may borrow another's) and owns
+// its cache regions or its state.  Three mixers, each behind ONE fused projection of the norm output: a matrix-state mixer with a decay
+// per key channel (attn_state.cu over the sequence slots), softmax attention whose scores are mixed over the heads before the softmax
+// (attn_heads.cu over the block table, K and V regions), and attention over a cached latent with a window and an output gate
+// (attn_latent.cu, absorbed form, one region).  Feed-forwards: a dense one, or experts named by a table row per token id.
+constexpr float TINEVIK_GATE_SHARP = 1.702f;   // expert: y = g * sigmoid(1.702 g) * (u + 1)
+
+int forward_mixed_list(b2_engine* e, int T, int ntiles, int nlast) {
+  const b2_config& c = e->cfg;
+  const int W = c.hidden, f = e->f32 ? 1 : 0;
+  cudaStream_t st = e->stream;
+  auto dbg = [&](int slot) {
+    if ((e->debug_flags & 1) && e->dbg_hidden_f32 != nullptr && T <= e->dbg_cap_tokens && slot < e->dbg_slots)
+      cudaMemcpyAsync(e->dbg_hidden_f32 + (size_t)slot * e->dbg_cap_tokens * W, e->l_h, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st);
+  };
+  auto dense = [&](const void* A, const void* Wt, float* C, int M, int N, int K) -> int { return list_dense(e, A, Wt, C, M, N, K, 1.f, st); };
+  {
+    KL k(e, B2K_EMBED);
+    if (!k.skip()) B2_TRY(launch_embed_scaled(e->d_tokens, e->l_embed, f, c.embed_scale != 0.f ? c.embed_scale : 1.f, e->l_h, T, W, c.vocab, st));
+  }
+  dbg(0);
+  const PrefillTile* tiles = ntiles > 0 ? e->d_tiles : nullptr;
+  const int portions = ntiles > 0 ? e->step_portions : T;
+  const int32_t* last_rows = ntiles > 0 ? e->d_last_rows : nullptr;
+  const bool use_tc = list_use_tc();
+  bool have_norm = false;   // l_x1 already holds this run's first norm output (the run before wrote it)
+  for (size_t r = 0; r < e->runs.size(); ++r) {
+    const ListRun& R = e->runs[r];
+    ListLayer& L = e->ll[R.layer];
+    const b2_layer_spec& sp = L.sp;
+    if (!have_norm) {
+      KL k(e, B2K_NORM);
+      if (!k.skip()) B2_TRY(launch_layer_norm(e->l_h, L.gain1, L.bias1, e->l_x1, f, T, W, c.rms_eps, nullptr, st));
+    }
+    {
+      KL k(e, B2K_GEMM_QKV);   // everything that reads the norm output: one projection
+      if (!k.skip()) B2_TRY(dense(e->l_x1, L.wqd, e->l_qd, T, L.nqd, W));
+    }
+    const int HV = sp.heads * sp.vdim;
+    if (sp.mixer == B2_MIXER_DECAY_STATE) {
+      const StateGeom sg{sp.heads, sp.heads, sp.dim, sp.vdim, STATE_RULE_DECAY};
+      {
+        KL k(e, B2K_ACT);   // decay per key channel: sigmoid(A2 (A1 n) + b)^(1 / tau)
+        if (!k.skip()) B2_TRY(launch_lowrank_act(e->l_qd, L.nqd, L.n_fixed, L.rank_a, L.a2, L.a2_bias, LOWRANK_DECAY_SIGMOID_POW, 1.0f / sp.s_tau, nullptr, 0,
+                                                 e->l_dec, T, sp.heads * sp.dim, st));
+      }
+      {
+        KL k(e, B2K_CHAIN);
+        if (!k.skip()) B2_TRY(launch_state_scan(e->l_qd + L.off_sq, L.nqd, e->l_qd + L.off_sk, L.nqd, e->l_qd + L.off_sv, L.nqd, e->l_dec, nullptr, sg,
+                                                1.0f / sqrtf((float)sp.dim), R.state, portions, last_rows, e->d_row_seq, e->d_row_first, e->d_row_end,
+                                                e->d_positions, e->d_slots, e->l_so, st));
+      }
+      {
+        KL k(e, B2K_ACT);   // per-head RMS norm of the read-out, times silu(g)
+        if (!k.skip()) B2_TRY(launch_state_out_gate(e->l_so, L.head_gain, e->l_qd + L.off_sg, L.nqd, 1, e->l_av, f, sp.heads, sp.vdim, c.rms_eps, T, st));
+      }
+    } else if (sp.mixer == B2_MIXER_MIXED_SCORE_ATTENTION) {
+      HeadsGeom g{sp.heads, sp.kv_heads, sp.dim, sp.vdim, sp.rot_dims, sp.rot_base, sp.scale, c.rms_eps, 0, 0, 0, 0.f, sp.window, 0, 0, 0};
+      g.rot_factor = sp.rot_factor;
+      g.rot_values = sp.rot_values;
+      g.softcap = sp.softcap;
+      char* kc = e->regions[R.k_region].base;
+      char* vc = e->regions[R.v_region].base;
+      {
+        KL k(e, B2K_ROPE_KV);
+        if (!k.skip()) B2_TRY(launch_heads_finish_halves(e->l_qd, L.nqd, g, L.qk_gain, L.qk_gain + sp.dim, e->d_positions, e->d_slots, e->l_q, kc, vc, f, T, st));
+      }
+      {
+        KL k(e, ntiles > 0 ? B2K_MISC : B2K_ATTN_DECODE);
+        if (!k.skip()) B2_TRY(launch_heads_attention_premix(e->l_q, kc, vc, f, g, sp.score_mix ? L.talk : nullptr, e->d_block_table, e->bt_stride, c.block_size,
+                                                            tiles, ntiles, e->d_positions, e->d_seq_lens, e->l_av, f, T, st));
+      }
+    } else {   // B2_MIXER_GATED_LATENT
+      const LatentGeom g{sp.heads, sp.dim, 0, sp.vdim, sp.kv_rank, 0, 0.f, sp.scale, c.rms_eps, sp.window};
+      char* cache = e->regions[R.k_region].base;
+      {
+        KL k(e, B2K_ROPE_KV);   // both latents normed: the query's becomes an operand, the other the token's cache row
+        if (!k.skip()) B2_TRY(launch_latent_pair_finish(e->l_qd, L.nqd, L.off_sq, sp.q_rank, L.off_sk, sp.kv_rank, L.latq_gain, L.lat_gain, c.rms_eps,
+                                                        e->d_slots, e->l_x2, cache, f, T, st));
+      }
+      {
+        KL k(e, B2K_GEMM_QKV);   // q of every head from its latent
+        if (!k.skip()) {
+          B2_TRY(dense(e->l_x2, L.uq, e->l_q, T, sp.heads * sp.dim, sp.q_rank));
+          B2_TRY(launch_store_rows(e->l_q, e->l_qnope, f, sp.heads * sp.dim, 0, T, sp.heads * sp.dim, st));
+        }
+      }
+      {
+        KL k(e, B2K_GEMM_QKV);   // the query pulled through the key up-projection, all heads in one strided batch
+        AnyGemm a;
+        a.A = e->l_qnope; a.W = L.ukT; a.C = e->l_qabs; a.M = T; a.N = sp.kv_rank; a.K = sp.dim;
+        a.lda = (long)sp.heads * sp.dim; a.ldw = sp.dim; a.ldc = (long)sp.heads * sp.kv_rank;
+        a.a_bs = sp.dim; a.w_bs = (long)sp.kv_rank * sp.dim; a.c_bs = sp.kv_rank;
+        if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, sp.heads, 0, st));
+      }
+      {
+        KL k(e, ntiles > 0 ? B2K_MISC : B2K_ATTN_DECODE);
+        if (!k.skip()) B2_TRY(launch_latent_attention(e->l_qabs, e->l_q, cache, f, g, e->d_block_table, e->bt_stride, c.block_size, tiles, ntiles, e->d_positions,
+                                                      e->d_seq_lens, nullptr, e->l_olat, f, T, st, e->l_attn_scratch, e->l_attn_scratch_floats, c.max_model_len));
+      }
+      {
+        KL k(e, B2K_GEMM_O);   // values of every head from the weighted latent (fp32 sums: the gate follows)
+        AnyGemm a;
+        a.A = e->l_olat; a.W = L.uv; a.C = e->l_so; a.M = T; a.N = sp.vdim; a.K = sp.kv_rank;
+        a.lda = (long)sp.heads * sp.kv_rank; a.ldw = sp.kv_rank; a.ldc = (long)HV;
+        a.a_bs = sp.kv_rank; a.w_bs = (long)sp.vdim * sp.kv_rank; a.c_bs = sp.vdim;
+        if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, sp.heads, 0, st));
+      }
+      {
+        KL k(e, B2K_ACT);
+        if (!k.skip()) B2_TRY(launch_sigmoid_gate(e->l_so, e->l_qd + L.off_sg, L.nqd, e->l_av, f, T, HV, st));
+      }
+    }
+    {
+      KL k(e, B2K_GEMM_O);
+      if (!k.skip()) B2_TRY(dense(e->l_av, L.wo, e->l_mix, T, W, HV));
+    }
+    const bool has_ff = sp.ff != B2_FF_NONE;
+    const ListLayer* NL = r + 1 < e->runs.size() ? &e->ll[e->runs[r + 1].layer] : nullptr;
+    const bool fuse_next = NL != nullptr && e->skip_mask == 0;
+    {
+      KL k(e, B2K_NORM);   // h += ln1b(mixer); the norm in front of the next sublayer in the same pass
+      const float* wn = has_ff ? L.gain2 : (fuse_next ? NL->gain1 : nullptr);
+      const float* bn = has_ff ? L.bias2 : (fuse_next ? NL->bias1 : nullptr);
+      if (!k.skip()) B2_TRY(launch_layer_norm_add(e->l_h, e->l_mix, nullptr, 0, 1.f, L.gain1b, L.bias1b, T, W, c.rms_eps, st, wn, bn, wn ? e->l_x1 : nullptr, f));
+      have_norm = !has_ff && fuse_next;
+    }
+    if (has_ff) {
+      const float* wn = fuse_next ? NL->gain1 : nullptr;
+      const float* bn = fuse_next ? NL->bias1 : nullptr;
+      if (sp.ff == B2_FF_XIELU) {
+        {
+          KL k(e, B2K_GEMM_GATEUP);
+          if (!k.skip()) B2_TRY(dense(e->l_x1, L.up, e->l_upf, T, sp.ff_dim, W));
+        }
+        {
+          KL k(e, B2K_ACT);
+          if (!k.skip()) B2_TRY(launch_xielu(e->l_upf, L.poly, e->l_act, f, (size_t)T * sp.ff_dim, st));
+        }
+        {
+          KL k(e, B2K_GEMM_DOWN);
+          if (!k.skip()) B2_TRY(dense(e->l_act, L.down, e->l_mix, T, W, sp.ff_dim));
+        }
+        {
+          KL k(e, B2K_NORM);
+          if (!k.skip()) B2_TRY(launch_layer_norm_add(e->l_h, e->l_mix, nullptr, 0, 1.f, L.gain2b, L.bias2b, T, W, c.rms_eps, st, wn, bn, wn ? e->l_x1 : nullptr, f));
+        }
+      } else {   // B2_FF_TABLE_EXPERTS
+        const int F = sp.ff_dim, pairs = T * sp.top;
+        {
+          KL k(e, B2K_ACT);
+          if (!k.skip()) B2_TRY(launch_route_table(e->d_tokens, L.table, c.vocab, sp.experts, sp.top, e->l_idx, e->l_rw, T, st));
+        }
+        {
+          KL k(e, B2K_MISC);
+          if (!k.skip()) B2_TRY(launch_route_permute(e->l_idx, T, sp.top, sp.experts, e->l_offsets, e->l_offsets_stride, e->l_slot_token, e->l_pair_slot, st));
+        }
+        // Prompt-sized bf16 steps run expert by expert on the tcgen05 projection kernel (rows gathered into expert order, the experts' slot
+        // ranges read back: one small copy and a stream synchronisation per layer); everything else as ragged groups.
+        const bool tc_experts = use_tc && !f && ntiles > 0 && e->l_xperm != nullptr && pairs >= LIST_TC_EXPERT_ROWS && W % 64 == 0 && F % 64 == 0 && W >= 128 &&
+                                F >= 64 && e->skip_mask == 0;
+        if (tc_experts) {
+          B2_CUDA_OK(cudaMemcpyAsync(e->h_offsets, e->l_offsets, (size_t)(sp.experts + 1) * 4, cudaMemcpyDeviceToHost, st));
+          {
+            KL k(e, B2K_MISC);
+            B2_TRY(launch_gather_rows((const bf16*)e->l_x1, e->l_slot_token, e->l_xperm, pairs, W, st));
+          }
+          B2_CUDA_OK(cudaStreamSynchronize(st));
+          const int32_t* off = e->h_offsets;
+          B2_REQUIRE(off[0] == 0 && off[sp.experts] == pairs, "layer %d: the experts' slot ranges do not cover the step's %d pairs", R.layer, pairs);
+          {
+            KL k(e, B2K_GEMM_GATEUP);
+            for (int x = 0; x < sp.experts; ++x)
+              if (off[x + 1] > off[x])
+                B2_TRY(dense(e->l_xperm + (size_t)off[x] * W, (const bf16*)L.up + (size_t)x * 2 * F * W, e->l_upf + (size_t)off[x] * 2 * F, off[x + 1] - off[x],
+                             2 * F, W));
+          }
+          {
+            KL k(e, B2K_ACT);
+            B2_TRY(launch_clamped_gate(e->l_upf, e->l_act, 0, pairs, F, sp.ff_limit, TINEVIK_GATE_SHARP, st));
+          }
+          {
+            KL k(e, B2K_GEMM_DOWN);
+            for (int x = 0; x < sp.experts; ++x)
+              if (off[x + 1] > off[x])
+                B2_TRY(dense((const bf16*)e->l_act + (size_t)off[x] * F, (const bf16*)L.down + (size_t)x * W * F, e->l_y + (size_t)off[x] * W,
+                             off[x + 1] - off[x], W, F));
+          }
+        } else {
+          const int max_tiles = std::min(e->l_tiles_cap, (pairs + any_gemm_tile_rows() - 1) / any_gemm_tile_rows() + sp.experts);
+          if (pairs > any_gemm_ragged_rows_limit() || W > 16384 || 2 * F > 16384) {
+            KL k(e, B2K_MISC);
+            if (!k.skip()) B2_TRY(launch_ragged_tiles(e->l_offsets, sp.experts, e->l_tile_group, e->l_tile_row0, e->l_ntiles, max_tiles, st));
+          }
+          AnyGemm a;
+          a.tile_group = e->l_tile_group; a.tile_row0 = e->l_tile_row0; a.n_tiles = e->l_ntiles; a.group_offsets = e->l_offsets;
+          {
+            KL k(e, B2K_GEMM_GATEUP);  // gate | up of every (token, choice) pair in expert order, fp32 sums
+            a.A = e->l_x1; a.a_rows = e->l_slot_token; a.W = L.up; a.C = e->l_upf; a.N = 2 * F; a.K = W; a.lda = W; a.ldw = W; a.ldc = 2 * F;
+            a.w_bs = (long)2 * F * W; a.epilogue = ANY_EPI_STORE;
+            if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, max_tiles, st, pairs, sp.experts));
+          }
+          {
+            KL k(e, B2K_ACT);
+            if (!k.skip()) B2_TRY(launch_clamped_gate(e->l_upf, e->l_act, f, pairs, F, sp.ff_limit, TINEVIK_GATE_SHARP, st));
+          }
+          {
+            KL k(e, B2K_GEMM_DOWN);
+            a.A = e->l_act; a.a_rows = nullptr; a.W = L.down; a.C = e->l_y; a.N = W; a.K = F; a.lda = F; a.ldw = F; a.ldc = W;
+            a.w_bs = (long)W * F; a.epilogue = ANY_EPI_STORE;
+            if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, max_tiles, st, pairs, sp.experts));
+          }
+        }
+        {
+          KL k(e, B2K_NORM);   // h += ln2b(mean of the token's experts)
+          if (!k.skip()) B2_TRY(launch_layer_norm_add(e->l_h, e->l_y, e->l_pair_slot, sp.top, 1.0f / (float)sp.top, L.gain2b, L.bias2b, T, W, c.rms_eps, st, wn, bn,
+                                                      wn ? e->l_x1 : nullptr, f));
+        }
+      }
+      have_norm = fuse_next;
+    }
+    dbg((int)r + 1);
+  }
+  {
+    KL k(e, B2K_NORM);
+    if (!k.skip()) B2_TRY(launch_layer_norm(e->l_h, e->l_final_gain, e->l_final_bias, e->l_xl, f, nlast, W, c.rms_eps, ntiles > 0 ? e->d_last_rows : nullptr, st));
+  }
+  {
+    KL k(e, B2K_LMHEAD);
+    if (!k.skip()) B2_TRY(list_dense(e, e->l_xl, e->l_head, e->l_logits, nlast, c.vocab, W, c.logit_scale != 0.f ? c.logit_scale : 1.f, st));
+  }
+  {
+    KL k(e, B2K_MISC);
+    bf16* lb = (e->debug_flags & 2) ? e->logits : nullptr;
+    if (!k.skip()) B2_TRY(launch_logits_finish(e->l_logits, e->d_out_tokens, lb, bucket_batch(std::max(c.max_seqs, 1)), nlast, c.vocab, e->v_pad, st));
+  }
+  return 0;
+}
+
 // Two-lane decode.  At batch 64 a decode step is two things that do not overlap when they depend on each other: the
 // attention pass of a layer (HBM-bound, about half the step) and the eight small kernels between two attention
 // passes (a chain of dependent launches that moves 31 MB of weights in ~30 us: latency-bound, HBM nearly idle).
@@ -1505,6 +1753,7 @@ int forward(b2_engine* e, int T, int ntiles, int nlast, int attn_split) {
   if (c.arch == B2_ARCH_LERASUN) return forward_list(e, T, ntiles, nlast);
   if (c.arch == B2_ARCH_KEDASUN) return forward_heads_list(e, T, ntiles, nlast);
   if (c.arch == B2_ARCH_BUMALIX) return forward_state_list(e, T, ntiles, nlast);
+  if (c.arch == B2_ARCH_TINEVIK) return forward_mixed_list(e, T, ntiles, nlast);
   if (c.arch == B2_ARCH_OPT) return forward_opt(e, T, ntiles, nlast);
   if (ntiles == 0 && e->use_chain == 2 && e->fused_ok && c.arch == B2_ARCH_QWEN3 && !(e->debug_flags & 1) &&
       e->force_gemm_impl != 0 && T > e->simt_max_tokens && T <= 64 && e->skip_mask == 0)
@@ -1887,9 +2136,10 @@ int list_tensor(b2_engine* e, const std::string& name, const void* host, size_t 
     return rc;
   };
   if (name == "embed") { B2_TRY(want((size_t)c.vocab * W)); return done(put_operand(e, e->l_embed, 0, src, (size_t)c.vocab * W)); }
-  if (name == "head") { B2_TRY(want((size_t)c.vocab * W)); return done(put_operand(e, e->l_head, 0, src, (size_t)c.vocab * W)); }
+  if (name == "head" && e->l_head != e->l_embed) { B2_TRY(want((size_t)c.vocab * W)); return done(put_operand(e, e->l_head, 0, src, (size_t)c.vocab * W)); }
   if (name == "embed.norm") { B2_TRY(want(W)); return done(put_f32(e->l_embed_gain, src, W, 1.0f)); }
   if (name == "final.norm") { B2_TRY(want(W)); return done(put_f32(e->l_final_gain, src, W, c.arch == B2_ARCH_LERASUN ? 1.0f : 0.0f)); }
+  if (name == "final.norm.b" && e->l_final_bias) { B2_TRY(want(W)); return done(put_f32(e->l_final_bias, src, W, 0.0f)); }
   if (c.arch == B2_ARCH_BUMALIX && name == "loop.in") {   // (a checkpoint may carry it although the config loops over nothing: nothing then uses it)
     B2_TRY(want(W * 2 * W));
     return done(e->l_loop_in ? put_operand(e, e->l_loop_in, 0, src, W * 2 * W) : 0);
@@ -1988,6 +2238,88 @@ int list_tensor(b2_engine* e, const std::string& name, const void* host, size_t 
             if (which == "up") { B2_TRY(want(ff * W)); return done(put_operand(e, L.up, ((size_t)ex * 2 + 1) * ff * W, src, ff * W)); }
             if (which == "down") { B2_TRY(want(W * ff)); return done(put_operand(e, L.down, (size_t)ex * W * ff, src, W * ff)); }
           }
+        }
+      }
+    }
+    b2_set_error("unknown tensor name %s", name.c_str());
+    return -22;
+  }
+  if (c.arch == B2_ARCH_TINEVIK) {
+    B2_REQUIRE(sp.weights_of < 0, "tensor %s: layer %d runs with layer %d's tensors and has none of its own", name.c_str(), li, sp.weights_of);
+    const size_t HV = H * dv;
+    if (rest == "norm1") { B2_TRY(want(W)); return done(put_f32(L.gain1, src, W, 0.0f)); }
+    if (rest == "norm1.b") { B2_TRY(want(W)); return done(put_f32(L.bias1, src, W, 0.0f)); }
+    if (rest == "norm1b") { B2_TRY(want(W)); return done(put_f32(L.gain1b, src, W, 0.0f)); }
+    if (rest == "norm1b.b") { B2_TRY(want(W)); return done(put_f32(L.bias1b, src, W, 0.0f)); }
+    if (sp.ff != B2_FF_NONE) {
+      if (rest == "norm2") { B2_TRY(want(W)); return done(put_f32(L.gain2, src, W, 0.0f)); }
+      if (rest == "norm2.b") { B2_TRY(want(W)); return done(put_f32(L.bias2, src, W, 0.0f)); }
+      if (rest == "norm2b") { B2_TRY(want(W)); return done(put_f32(L.gain2b, src, W, 0.0f)); }
+      if (rest == "norm2b.b") { B2_TRY(want(W)); return done(put_f32(L.bias2b, src, W, 0.0f)); }
+    }
+    if (rest == "mix.o") { B2_TRY(want(W * HV)); return done(put_operand(e, L.wo, 0, src, W * HV)); }
+    if (sp.mixer == B2_MIXER_DECAY_STATE) {
+      if (rest == "mix.q") { B2_TRY(want(H * dn * W)); return done(put_operand(e, L.wqd, (size_t)L.off_sq * W, src, H * dn * W)); }
+      if (rest == "mix.k") { B2_TRY(want(H * dn * W)); return done(put_operand(e, L.wqd, (size_t)L.off_sk * W, src, H * dn * W)); }
+      if (rest == "mix.v") { B2_TRY(want(HV * W)); return done(put_operand(e, L.wqd, (size_t)L.off_sv * W, src, HV * W)); }
+      if (rest == "mix.g") { B2_TRY(want(HV * W)); return done(put_operand(e, L.wqd, (size_t)L.off_sg * W, src, HV * W)); }
+      if (rest == "mix.norm") { B2_TRY(want(dv)); return done(put_f32(L.head_gain, src, dv, 0.0f)); }
+      if (rest == "mix.a2.b") { B2_TRY(want(H * dn)); return done(put_f32(L.a2_bias, src, H * dn, 0.0f)); }
+      if (rest == "mix.a1") {   // [rank][W], the rank from the size: it joins the fused projection when the weights are finalised
+        B2_REQUIRE(nbytes >= 2 * W && nbytes % (2 * W) == 0, "tensor %s: %zu bytes are not rows of %zu values", name.c_str(), nbytes, W);
+        B2_REQUIRE(L.nqd == L.n_fixed, "tensor %s: the layer's projection is already joined", name.c_str());
+        L.a1_host.assign(src, src + nbytes / 2);
+        L.rank_a = (int)(nbytes / (2 * W));
+        return done(0);
+      }
+      if (rest == "mix.a2") {
+        B2_REQUIRE(nbytes >= 2 && nbytes % 2 == 0, "tensor %s: %zu bytes", name.c_str(), nbytes);
+        if (L.a2) cudaFree(L.a2);
+        L.a2 = nullptr;
+        B2_TRY(dalloc(&L.a2, nbytes / 2));
+        L.a2_floats = nbytes / 2;
+        e->weight_bytes += (int64_t)(nbytes * 2);
+        return done(put_f32(L.a2, src, nbytes / 2, 0.0f));
+      }
+    } else if (sp.mixer == B2_MIXER_MIXED_SCORE_ATTENTION) {
+      const size_t nq = L.nq, nk = L.nk, nv = L.nv;
+      if (rest == "mix.q") { B2_TRY(want(nq * W)); return done(put_operand(e, L.wqd, 0, src, nq * W)); }
+      if (rest == "mix.k") { B2_TRY(want(nk * W)); return done(put_operand(e, L.wqd, nq * W, src, nk * W)); }
+      if (rest == "mix.v") { B2_TRY(want(nv * W)); return done(put_operand(e, L.wqd, (nq + nk) * W, src, nv * W)); }
+      if (rest == "mix.q.norm") { B2_TRY(want(dn)); return done(put_f32(L.qk_gain, src, dn, 0.0f)); }
+      if (rest == "mix.k.norm") { B2_TRY(want(dn)); return done(put_f32(L.qk_gain + dn, src, dn, 0.0f)); }
+      if (rest == "mix.talk") { B2_TRY(want(H * H)); return done(put_f32(L.talk, src, H * H, 0.0f)); }
+    } else {
+      const size_t qr = sp.q_rank;
+      if (rest == "mix.dq") { B2_TRY(want(qr * W)); return done(put_operand(e, L.wqd, (size_t)L.off_sq * W, src, qr * W)); }
+      if (rest == "mix.dkv") { B2_TRY(want(r * W)); return done(put_operand(e, L.wqd, (size_t)L.off_sk * W, src, r * W)); }
+      if (rest == "mix.g") { B2_TRY(want(HV * W)); return done(put_operand(e, L.wqd, (size_t)L.off_sg * W, src, HV * W)); }
+      if (rest == "mix.dq.norm") { B2_TRY(want(qr)); return done(put_f32(L.latq_gain, src, qr, 0.0f)); }
+      if (rest == "mix.dkv.norm") { B2_TRY(want(r)); return done(put_f32(L.lat_gain, src, r, 0.0f)); }
+      if (rest == "mix.uq") { B2_TRY(want(H * dn * qr)); return done(put_operand(e, L.uq, 0, src, H * dn * qr)); }
+      if (rest == "mix.uk") {  // stored [heads * dim][kv_rank]; kept per head as [kv_rank][dim], the layout the absorbed-query product reads
+        B2_TRY(want(H * dn * r));
+        std::vector<uint16_t> tr(H * dn * r);
+        for (size_t a = 0; a < H; ++a)
+          for (size_t d = 0; d < dn; ++d)
+            for (size_t j = 0; j < r; ++j) tr[(a * r + j) * dn + d] = src[(a * dn + d) * r + j];
+        return done(put_operand(e, L.ukT, 0, tr.data(), tr.size()));
+      }
+      if (rest == "mix.uv") { B2_TRY(want(HV * r)); return done(put_operand(e, L.uv, 0, src, HV * r)); }
+    }
+    if (sp.ff == B2_FF_XIELU) {
+      if (rest == "mlp.up") { B2_TRY(want(ff * W)); return done(put_operand(e, L.up, 0, src, ff * W)); }
+      if (rest == "mlp.down") { B2_TRY(want(W * ff)); return done(put_operand(e, L.down, 0, src, W * ff)); }
+      if (rest == "mlp.act") { B2_TRY(want(2)); return done(put_f32(L.poly, src, 2, 0.0f)); }
+    } else if (sp.ff == B2_FF_TABLE_EXPERTS && rest.compare(0, 5, "mlp.e") == 0) {
+      size_t d2 = rest.find('.', 5);
+      if (d2 != std::string::npos) {
+        const int ex = atoi(rest.substr(5, d2 - 5).c_str());
+        const std::string which = rest.substr(d2 + 1);
+        if (ex >= 0 && ex < sp.experts) {   // gate rows, then up rows, expert by expert: one product gives both
+          if (which == "gate") { B2_TRY(want(ff * W)); return done(put_operand(e, L.up, (size_t)ex * 2 * ff * W, src, ff * W)); }
+          if (which == "up") { B2_TRY(want(ff * W)); return done(put_operand(e, L.up, ((size_t)ex * 2 + 1) * ff * W, src, ff * W)); }
+          if (which == "down") { B2_TRY(want(W * ff)); return done(put_operand(e, L.down, (size_t)ex * W * ff, src, W * ff)); }
         }
       }
     }
@@ -2433,8 +2765,8 @@ std::vector<std::string> state_tensor_names(const b2_engine* e) {
 }
 
 // Every tensor is in: the low-rank first stages join the fused projections, and the buffer the projections write is sized.
+int join_low_rank(b2_engine* e, ListLayer& L);
 int state_finalize(b2_engine* e) {
-  const size_t W = e->cfg.hidden;
   for (const std::string& name : state_tensor_names(e)) B2_REQUIRE(e->loaded.count(name), "weights incomplete: %s missing", name.c_str());
   size_t max_nqd = 1;
   for (size_t l = 0; l < e->ll.size(); ++l) {
@@ -2445,21 +2777,307 @@ int state_finalize(b2_engine* e) {
     B2_REQUIRE(L.rank_a >= 1 && L.a2_floats == dec * L.rank_a, "layer %zu: a1 has %d rows, a2 %zu numbers for %zu channels", l, L.rank_a, L.a2_floats, dec);
     B2_REQUIRE(two || (L.rank_g >= 1 && L.g2_floats == (size_t)sp.heads * sp.vdim * L.rank_g), "layer %zu: g1 has %d rows, g2 %zu numbers", l, L.rank_g,
                L.g2_floats);
-    if (L.nqd == L.n_fixed) {   // (not yet joined: finalize may be called again after more tensors)
-      const size_t rows = (size_t)L.n_fixed + L.rank_a + L.rank_g;
-      char* fused = nullptr;
-      B2_TRY(dalloc(&fused, rows * W * e->esz));
-      B2_CUDA_OK(cudaMemcpy(fused, L.wqd, (size_t)L.n_fixed * W * e->esz, cudaMemcpyDeviceToDevice));
-      B2_TRY(put_operand(e, fused, (size_t)L.n_fixed * W, L.a1_host.data(), L.a1_host.size()));
-      if (L.rank_g > 0) B2_TRY(put_operand(e, fused, ((size_t)L.n_fixed + L.rank_a) * W, L.g1_host.data(), L.g1_host.size()));
-      cudaFree(L.wqd);
-      L.wqd = fused;
-      L.nqd = (int)rows;
-      e->weight_bytes += (int64_t)((rows - L.n_fixed) * W * e->esz);
-      L.a1_host.clear();
-      L.a1_host.shrink_to_fit();
-      L.g1_host.clear();
-      L.g1_host.shrink_to_fit();
+    B2_TRY(join_low_rank(e, L));
+    max_nqd = std::max(max_nqd, (size_t)L.nqd);
+  }
+  if (e->l_qd == nullptr || max_nqd > e->l_qd_cols) {
+    if (e->l_qd) cudaFree(e->l_qd);
+    e->l_qd = nullptr;
+    B2_TRY(dalloc(&e->l_qd, (size_t)e->cap_tokens * max_nqd));
+    e->l_qd_cols = max_nqd;
+  }
+  return 0;
+}
+
+// Integer tensors of a checkpoint (int32): the table that names every token id's experts.
+int list_int_tensor(b2_engine* e, const std::string& name, const int32_t* host, size_t count) {
+  const b2_config& c = e->cfg;
+  size_t dot = name.find('.');
+  B2_REQUIRE(c.arch == B2_ARCH_TINEVIK && name.size() >= 3 && name[0] == 'l' && dot != std::string::npos && dot >= 2, "integer tensor %s: no model of this family has it",
+             name.c_str());
+  const int li = atoi(name.substr(1, dot - 1).c_str());
+  B2_REQUIRE(li >= 0 && li < c.num_layers, "tensor %s: layer out of range", name.c_str());
+  ListLayer& L = e->ll[li];
+  B2_REQUIRE(name.substr(dot + 1) == "mlp.table" && L.sp.ff == B2_FF_TABLE_EXPERTS && L.table != nullptr, "unknown integer tensor %s", name.c_str());
+  B2_REQUIRE(count == (size_t)c.vocab * L.sp.top, "tensor %s: expected %zu entries, got %zu", name.c_str(), (size_t)c.vocab * L.sp.top, count);
+  for (size_t i = 0; i < count; ++i)
+    B2_REQUIRE(host[i] >= 0 && host[i] < L.sp.experts, "tensor %s: entry %zu names expert %d of %d", name.c_str(), i, host[i], L.sp.experts);
+  B2_CUDA_OK(cudaMemcpy(L.table, host, count * 4, cudaMemcpyHostToDevice));
+  e->loaded[name] = 1;
+  return 0;
+}
+
+// The low-rank first stages of a layer (their widths came with the tensors) join its fused projection behind the n_fixed rows whose count
+// the config gives.
+int join_low_rank(b2_engine* e, ListLayer& L) {
+  const size_t W = e->cfg.hidden;
+  if (L.nqd != L.n_fixed) return 0;   // (already joined: finalize may be called again after more tensors)
+  const size_t rows = (size_t)L.n_fixed + L.rank_a + L.rank_g;
+  char* fused = nullptr;
+  B2_TRY(dalloc(&fused, rows * W * e->esz));
+  B2_CUDA_OK(cudaMemcpy(fused, L.wqd, (size_t)L.n_fixed * W * e->esz, cudaMemcpyDeviceToDevice));
+  B2_TRY(put_operand(e, fused, (size_t)L.n_fixed * W, L.a1_host.data(), L.a1_host.size()));
+  if (L.rank_g > 0) B2_TRY(put_operand(e, fused, ((size_t)L.n_fixed + L.rank_a) * W, L.g1_host.data(), L.g1_host.size()));
+  cudaFree(L.wqd);
+  L.wqd = fused;
+  L.nqd = (int)rows;
+  e->weight_bytes += (int64_t)((rows - L.n_fixed) * W * e->esz);
+  L.a1_host.clear();
+  L.a1_host.shrink_to_fit();
+  L.g1_host.clear();
+  L.g1_host.shrink_to_fit();
+  return 0;
+}
+
+// The same for the family whose layers mix three kinds of mixers and two kinds of feed-forwards, with layer norms around every sublayer and
+// layers that run with another layer's tensors (Tinevik).
+int mixed_engine_alloc(b2_engine* e) {
+  const b2_config& c = e->cfg;
+  const size_t W = c.hidden, es = e->esz;
+  B2_REQUIRE(!e->specs.empty() && (int)e->specs.size() == c.num_layers, "Tinevik: layer_specs missing");
+  B2_REQUIRE(c.hidden >= 1 && c.vocab >= 1 && c.num_layers >= 1, "Tinevik: bad sizes");
+  auto xalloc = [&](void** p, size_t elems) -> int {
+    char* q = nullptr;
+    B2_TRY(dalloc(&q, std::max<size_t>(elems, 1) * es));
+    *p = q;
+    e->weight_bytes += (int64_t)(elems * es);
+    return 0;
+  };
+  auto falloc = [&](float** p, size_t n) -> int {
+    B2_TRY(dalloc(p, std::max<size_t>(n, 1)));
+    B2_CUDA_OK(cudaMemset(*p, 0, std::max<size_t>(n, 1) * 4));
+    e->weight_bytes += (int64_t)(n * 4);
+    return 0;
+  };
+  e->weight_bytes = 0;
+  B2_TRY(xalloc(&e->l_embed, (size_t)c.vocab * W));
+  if (c.tie_embeddings) e->l_head = e->l_embed;   // the embedding table itself is the head
+  else B2_TRY(xalloc(&e->l_head, (size_t)c.vocab * W));
+  B2_TRY(falloc(&e->l_final_gain, W));
+  B2_TRY(falloc(&e->l_final_bias, W));
+  e->ll.resize(c.num_layers);
+  size_t max_q = 1, max_dec = 1, max_hv = 1, max_up = 1, max_act = 1, max_qr = 1, max_hr = 1, max_hd = 1;
+  int max_top = 1, max_exp = 1, max_heads = 1, max_rank = 1;
+  bool any_latent = false, any_experts = false;
+  for (int l = 0; l < c.num_layers; ++l) {
+    ListLayer& L = e->ll[l];
+    L.sp = e->specs[l];
+    const b2_layer_spec& sp = L.sp;
+    B2_REQUIRE(sp.mixer == B2_MIXER_DECAY_STATE || sp.mixer == B2_MIXER_MIXED_SCORE_ATTENTION || sp.mixer == B2_MIXER_GATED_LATENT,
+               "layer %d: mixer kind %d not built for this family", l, sp.mixer);
+    B2_REQUIRE(sp.heads >= 1 && sp.dim >= 1 && sp.vdim >= 1, "layer %d: bad mixer sizes (heads %d, dim %d, vdim %d)", l, sp.heads, sp.dim, sp.vdim);
+    B2_REQUIRE(sp.ff == B2_FF_NONE || (sp.ff == B2_FF_XIELU && sp.ff_dim >= 1) ||
+                   (sp.ff == B2_FF_TABLE_EXPERTS && sp.ff_dim >= 1 && sp.experts >= 1 && sp.top >= 1 && sp.top <= sp.experts),
+               "layer %d: feed-forward kind %d (ff %d, experts %d, top %d) not built for this family", l, sp.ff, sp.ff_dim, sp.experts, sp.top);
+    const size_t HV = (size_t)sp.heads * sp.vdim;
+    max_hv = std::max(max_hv, HV);
+    if (sp.mixer == B2_MIXER_DECAY_STATE) {
+      B2_REQUIRE(sp.dim <= 256 && sp.s_tau > 0.f, "layer %d: a state mixer needs a key width of at most 256 (%d) and tau > 0 (%g)", l, sp.dim, (double)sp.s_tau);
+      max_dec = std::max(max_dec, (size_t)sp.heads * sp.dim);
+    } else if (sp.mixer == B2_MIXER_MIXED_SCORE_ATTENTION) {
+      B2_REQUIRE(sp.kv_heads >= 1 && sp.heads % sp.kv_heads == 0, "layer %d: %d heads over %d key/value heads", l, sp.heads, sp.kv_heads);
+      B2_REQUIRE(sp.rot_dims >= 0 && sp.rot_dims <= sp.dim && sp.rot_dims % 2 == 0, "layer %d: rot dims %d must be even and <= dim %d", l, sp.rot_dims, sp.dim);
+      B2_REQUIRE(!sp.rot_values || sp.vdim % 2 == 0, "layer %d: rotated values need an even vdim (%d)", l, sp.vdim);
+      max_q = std::max(max_q, (size_t)sp.heads * sp.dim);
+    } else {
+      B2_REQUIRE(sp.kv_rank >= 1 && sp.q_rank >= 1 && sp.window >= 0, "layer %d: bad latent sizes (kv_rank %d, q_rank %d)", l, sp.kv_rank, sp.q_rank);
+      any_latent = true;
+      max_q = std::max(max_q, (size_t)sp.heads * sp.dim);
+      max_hd = std::max(max_hd, (size_t)sp.heads * sp.dim);
+      max_qr = std::max(max_qr, (size_t)sp.q_rank);
+      max_hr = std::max(max_hr, (size_t)sp.heads * sp.kv_rank);
+      max_heads = std::max(max_heads, sp.heads);
+      max_rank = std::max(max_rank, sp.kv_rank);
+    }
+    if (sp.ff == B2_FF_XIELU) {
+      max_up = std::max(max_up, (size_t)sp.ff_dim);
+      max_act = std::max(max_act, (size_t)sp.ff_dim);
+    } else if (sp.ff == B2_FF_TABLE_EXPERTS) {
+      any_experts = true;
+      max_top = std::max(max_top, sp.top);
+      max_exp = std::max(max_exp, sp.experts);
+      max_up = std::max(max_up, (size_t)sp.top * 2 * sp.ff_dim);
+      max_act = std::max(max_act, (size_t)sp.top * sp.ff_dim);
+    }
+    if (sp.weights_of >= 0) {   // the layer runs with another layer's tensors: the same kinds and sizes, nothing of its own to hold
+      B2_REQUIRE(sp.weights_of < c.num_layers && sp.weights_of != l && e->specs[sp.weights_of].weights_of < 0, "layer %d: weights_of %d must name a layer with tensors of its own",
+                 l, sp.weights_of);
+      const b2_layer_spec& o = e->specs[sp.weights_of];
+      B2_REQUIRE(o.mixer == sp.mixer && o.heads == sp.heads && o.kv_heads == sp.kv_heads && o.dim == sp.dim && o.vdim == sp.vdim && o.kv_rank == sp.kv_rank &&
+                     o.q_rank == sp.q_rank && o.ff == sp.ff && o.ff_dim == sp.ff_dim && o.experts == sp.experts && o.top == sp.top,
+                 "layer %d: its sizes differ from those of layer %d whose tensors it uses", l, sp.weights_of);
+      continue;
+    }
+    B2_TRY(falloc(&L.gain1, W));
+    B2_TRY(falloc(&L.bias1, W));
+    B2_TRY(falloc(&L.gain1b, W));
+    B2_TRY(falloc(&L.bias1b, W));
+    B2_TRY(xalloc(&L.wo, W * HV));
+    if (sp.mixer == B2_MIXER_DECAY_STATE) {
+      L.off_sq = 0;
+      L.off_sk = sp.heads * sp.dim;
+      L.off_sv = 2 * sp.heads * sp.dim;
+      L.off_sg = L.off_sv + (int)HV;
+      L.n_fixed = L.off_sg + (int)HV;
+      B2_TRY(falloc(&L.head_gain, sp.vdim));
+      B2_TRY(falloc(&L.a2_bias, (size_t)sp.heads * sp.dim));
+    } else if (sp.mixer == B2_MIXER_MIXED_SCORE_ATTENTION) {
+      L.nq = sp.heads * sp.dim;
+      L.nk = sp.kv_heads * sp.dim;
+      L.nv = sp.kv_heads * sp.vdim;
+      L.n_fixed = L.nq + L.nk + L.nv;
+      B2_TRY(falloc(&L.qk_gain, (size_t)2 * sp.dim));
+      B2_TRY(falloc(&L.talk, (size_t)sp.heads * sp.heads));
+    } else {
+      L.off_sq = 0;
+      L.off_sk = sp.q_rank;
+      L.off_sg = sp.q_rank + sp.kv_rank;
+      L.n_fixed = L.off_sg + (int)HV;
+      B2_TRY(falloc(&L.latq_gain, sp.q_rank));
+      B2_TRY(falloc(&L.lat_gain, sp.kv_rank));
+      B2_TRY(xalloc(&L.uq, (size_t)sp.heads * sp.dim * sp.q_rank));
+      B2_TRY(xalloc(&L.ukT, (size_t)sp.heads * sp.kv_rank * sp.dim));
+      B2_TRY(xalloc(&L.uv, HV * sp.kv_rank));
+    }
+    L.nqd = L.n_fixed;
+    B2_TRY(xalloc(&L.wqd, (size_t)L.n_fixed * W));
+    if (sp.ff != B2_FF_NONE) {
+      B2_TRY(falloc(&L.gain2, W));
+      B2_TRY(falloc(&L.bias2, W));
+      B2_TRY(falloc(&L.gain2b, W));
+      B2_TRY(falloc(&L.bias2b, W));
+    }
+    if (sp.ff == B2_FF_XIELU) {
+      B2_TRY(xalloc(&L.up, (size_t)sp.ff_dim * W));
+      B2_TRY(xalloc(&L.down, W * sp.ff_dim));
+      B2_TRY(falloc(&L.poly, 2));
+    } else if (sp.ff == B2_FF_TABLE_EXPERTS) {
+      B2_TRY(xalloc(&L.up, (size_t)sp.experts * 2 * sp.ff_dim * W));
+      B2_TRY(xalloc(&L.down, (size_t)sp.experts * W * sp.ff_dim));
+      B2_TRY(dalloc(&L.table, (size_t)c.vocab * sp.top));
+      B2_CUDA_OK(cudaMemset(L.table, 0, (size_t)c.vocab * sp.top * 4));
+      e->weight_bytes += (int64_t)c.vocab * sp.top * 4;
+    }
+  }
+  // ---- the runs: one per listed layer, with the layer whose tensors it uses and a state of its own ----
+  for (int l = 0; l < c.num_layers; ++l) {
+    ListRun R;
+    R.layer = e->specs[l].weights_of >= 0 ? e->specs[l].weights_of : l;
+    const b2_layer_spec& sp = e->ll[R.layer].sp;
+    if (sp.mixer == B2_MIXER_DECAY_STATE) {
+      const StateGeom sg{sp.heads, sp.heads, sp.dim, sp.vdim, 0};
+      const size_t sf = (size_t)c.max_seqs * state_floats_per_slot(sg);
+      B2_TRY(dalloc(&R.state, sf));
+      B2_CUDA_OK(cudaMemset(R.state, 0, sf * 4));
+      e->l_has_state = true;
+    }
+    e->runs.push_back(R);
+  }
+  e->dbg_slots = (int)e->runs.size() + 1;
+  // ---- activations ----
+  e->cap_tokens = ((std::max(c.max_batch_tokens, c.max_seqs) + 255) / 256) * 256;
+  const size_t Tc = e->cap_tokens;
+  e->l_rows_cap = (int)(Tc + bucket_batch(c.max_seqs));
+  e->l_max_top = max_top;
+  e->v_pad = (c.vocab + 7) / 8 * 8;
+  auto aalloc = [&](void** p, size_t elems) -> int {
+    char* q = nullptr;
+    B2_TRY(dalloc(&q, elems * es));
+    *p = q;
+    return 0;
+  };
+  B2_TRY(dalloc(&e->l_h, Tc * W));
+  B2_TRY(dalloc(&e->l_q, Tc * max_q));
+  B2_TRY(dalloc(&e->l_dec, Tc * max_dec));
+  B2_TRY(dalloc(&e->l_so, Tc * max_hv));
+  B2_TRY(dalloc(&e->l_mix, Tc * W));
+  B2_TRY(dalloc(&e->l_upf, Tc * max_up));
+  B2_TRY(dalloc(&e->l_logits, (size_t)e->l_rows_cap * c.vocab));
+  B2_TRY(aalloc(&e->l_x1, Tc * W));
+  B2_TRY(aalloc(&e->l_av, Tc * max_hv));
+  B2_TRY(aalloc(&e->l_act, Tc * max_act));
+  B2_TRY(aalloc(&e->l_xl, (size_t)e->l_rows_cap * W));
+  if (any_latent) {
+    B2_TRY(aalloc(&e->l_x2, Tc * max_qr));
+    B2_TRY(aalloc(&e->l_qnope, Tc * max_hd));
+    B2_TRY(dalloc(&e->l_qabs, Tc * max_hr));
+    B2_TRY(aalloc(&e->l_olat, Tc * max_hr));
+    if (!e->f32) {
+      e->l_attn_scratch_floats = latent_attention_scratch_floats(bucket_batch(c.max_seqs), max_heads, max_rank);
+      B2_TRY(dalloc(&e->l_attn_scratch, e->l_attn_scratch_floats));
+    }
+  }
+  if (any_experts) {
+    B2_TRY(dalloc(&e->l_y, Tc * max_top * W));
+    B2_TRY(dalloc(&e->l_rw, Tc * max_top));
+    B2_TRY(dalloc(&e->l_idx, Tc * max_top));
+    e->l_offsets_stride = max_exp + 1;
+    B2_TRY(dalloc(&e->l_offsets, (size_t)3 * (max_exp + 1)));
+    B2_CUDA_OK(cudaMemset(e->l_offsets, 0, (size_t)3 * (max_exp + 1) * 4));
+    B2_TRY(dalloc(&e->l_slot_token, Tc * max_top));
+    B2_TRY(dalloc(&e->l_pair_slot, Tc * max_top));
+    e->l_tiles_cap = (int)(Tc * max_top / any_gemm_tile_rows() + max_exp + 1);
+    B2_TRY(dalloc(&e->l_tile_group, (size_t)e->l_tiles_cap));
+    B2_TRY(dalloc(&e->l_tile_row0, (size_t)e->l_tiles_cap));
+    B2_TRY(dalloc(&e->l_ntiles, (size_t)1));
+    if (!e->f32 && Tc * max_top >= (size_t)LIST_TC_EXPERT_ROWS && max_exp > 1) {   // prompt-sized expert products on the tcgen05 projection kernel
+      B2_TRY(dalloc(&e->l_xperm, Tc * max_top * W));
+      B2_CUDA_OK(cudaMallocHost(&e->h_offsets, (size_t)(max_exp + 1) * sizeof(int32_t)));
+    }
+    B2_CUDA_OK(cudaMemset(e->l_ntiles, 0, 4));
+    B2_CUDA_OK(cudaMemset(e->l_pair_slot, 0, Tc * max_top * 4));
+  }
+  B2_TRY(dalloc(&e->d_row_seq, Tc));
+  B2_TRY(dalloc(&e->d_row_first, Tc));
+  B2_TRY(dalloc(&e->d_row_end, Tc));
+  B2_CUDA_OK(cudaMemset(e->d_row_seq, 0, Tc * 4));
+  B2_CUDA_OK(cudaMemset(e->d_row_first, 0, Tc * 4));
+  B2_CUDA_OK(cudaMemset(e->d_row_end, 0, Tc * 4));
+  return 0;
+}
+
+// Names of the tensors a Tinevik checkpoint must hold (layers that use another layer's tensors have none).
+std::vector<std::string> mixed_tensor_names(const b2_engine* e) {
+  std::vector<std::string> n = {"embed", "final.norm", "final.norm.b"};
+  if (e->l_head != e->l_embed) n.push_back("head");
+  for (size_t l = 0; l < e->ll.size(); ++l) {
+    const b2_layer_spec& sp = e->ll[l].sp;
+    if (sp.weights_of >= 0) continue;
+    const std::string p = "l" + std::to_string(l) + ".";
+    for (const char* t : {"norm1", "norm1.b", "norm1b", "norm1b.b"}) n.push_back(p + t);
+    if (sp.mixer == B2_MIXER_DECAY_STATE) {
+      for (const char* t : {"q", "k", "v", "g", "o", "norm", "a1", "a2", "a2.b"}) n.push_back(p + "mix." + t);
+    } else if (sp.mixer == B2_MIXER_MIXED_SCORE_ATTENTION) {
+      for (const char* t : {"q", "k", "v", "o", "q.norm", "k.norm"}) n.push_back(p + "mix." + t);
+      if (sp.score_mix) n.push_back(p + "mix.talk");
+    } else {
+      for (const char* t : {"dq", "dq.norm", "uq", "dkv", "dkv.norm", "uk", "uv", "g", "o"}) n.push_back(p + "mix." + t);
+    }
+    if (sp.ff != B2_FF_NONE)
+      for (const char* t : {"norm2", "norm2.b", "norm2b", "norm2b.b"}) n.push_back(p + t);
+    if (sp.ff == B2_FF_XIELU) {
+      for (const char* t : {"up", "down", "act"}) n.push_back(p + "mlp." + t);
+    } else if (sp.ff == B2_FF_TABLE_EXPERTS) {
+      n.push_back(p + "mlp.table");
+      for (int x = 0; x < sp.experts; ++x)
+        for (const char* t : {"gate", "up", "down"}) n.push_back(p + "mlp.e" + std::to_string(x) + "." + t);
+    }
+  }
+  return n;
+}
+
+// Every tensor is in: the low-rank first stages join the fused projections, and the buffer the projections write is sized.
+int mixed_finalize(b2_engine* e) {
+  for (const std::string& name : mixed_tensor_names(e)) B2_REQUIRE(e->loaded.count(name), "weights incomplete: %s missing", name.c_str());
+  size_t max_nqd = 1;
+  for (size_t l = 0; l < e->ll.size(); ++l) {
+    ListLayer& L = e->ll[l];
+    const b2_layer_spec& sp = L.sp;
+    if (sp.weights_of >= 0) continue;
+    if (sp.mixer == B2_MIXER_DECAY_STATE) {
+      const size_t dec = (size_t)sp.heads * sp.dim;
+      B2_REQUIRE(L.rank_a >= 1 && L.a2_floats == dec * L.rank_a, "layer %zu: a1 has %d rows, a2 %zu numbers for %zu channels", l, L.rank_a, L.a2_floats, dec);
+      B2_TRY(join_low_rank(e, L));
     }
     max_nqd = std::max(max_nqd, (size_t)L.nqd);
   }
@@ -2474,6 +3092,7 @@ int state_finalize(b2_engine* e) {
 
 // Validates the layer list and allocates weights, activations and scratch of a layer-list engine.
 int list_engine_alloc(b2_engine* e) {
+  if (e->cfg.arch == B2_ARCH_TINEVIK) return mixed_engine_alloc(e);
   if (e->cfg.arch == B2_ARCH_BUMALIX) return state_engine_alloc(e);
   if (e->cfg.arch == B2_ARCH_KEDASUN) return heads_engine_alloc(e);
   const b2_config& c = e->cfg;
@@ -2829,8 +3448,13 @@ int load_safetensors(b2_engine* e, const char* path) {
         }
         src = conv.data();
         nbytes = n * 2;
+      } else if (dt->as_string() == "I32") {   // integer tables (the layer-list families that have one)
+        rc = list_arch(e->cfg.arch) ? list_int_tensor(e, kv.first, reinterpret_cast<const int32_t*>(src), nbytes / 4)
+                                    : (b2_set_error("tensor %s: this family has no integer tensors", kv.first.c_str()), -22);
+        if (rc != 0) break;
+        continue;
       } else if (dt->as_string() != "BF16") {
-        throw std::runtime_error("tensor " + kv.first + ": dtype " + dt->as_string() + " not supported (BF16/F16/F32)");
+        throw std::runtime_error("tensor " + kv.first + ": dtype " + dt->as_string() + " not supported (BF16/F16/F32/I32)");
       }
       if (kv.first.find("rotary_emb.inv_freq") != std::string::npos) continue;
       rc = layer_tensor(e, kv.first, src, nbytes);
@@ -2853,7 +3477,7 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
   B2_REQUIRE(cfg != nullptr && out != nullptr, "b2_engine_create: null argument");
   B2_REQUIRE(cfg->abi_version == B2_ABI_VERSION, "b2_engine_create: abi_version %d != %d", cfg->abi_version, B2_ABI_VERSION);
   B2_REQUIRE(cfg->arch == B2_ARCH_QWEN3 || cfg->arch == B2_ARCH_PHI3 || cfg->arch == B2_ARCH_OPT || list_arch(cfg->arch),
-             "arch %d not built (0 = Qwen3, 1 = Phi-3, 2 = OPT, 3 = Lerasun, 4 = Kedasun, 5 = Bumalix)", cfg->arch);
+             "arch %d not built (0 = Qwen3, 1 = Phi-3, 2 = OPT, 3 = Lerasun, 4 = Kedasun, 5 = Bumalix, 6 = Tinevik)", cfg->arch);
   const bool ls = list_arch(cfg->arch);  // a layer-list family: its sizes live in layer_specs and are checked in list_engine_alloc
   B2_REQUIRE(ls || !cfg->compute_f32, "compute_f32: only the layer-list families have an fp32 path");
   B2_REQUIRE(!ls || cfg->layer_specs != nullptr, "layer-list family: layer_specs is NULL");
@@ -3119,10 +3743,19 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
       size_t page_bytes_all = blk_elems * 2 * 2 * c.num_layers;
       const bool heads_cache = c.arch == B2_ARCH_KEDASUN;  // a K region and a V region per layer, rows of kv_heads * dim / kv_heads * vdim
       const bool state_arch = c.arch == B2_ARCH_BUMALIX;   // a K and a V region per RUN of a layer that has a softmax mixer
+      const bool mixed_arch = c.arch == B2_ARCH_TINEVIK;   // per RUN: a K and a V region for a softmax mixer, one region of latents for a latent mixer
       if (state_arch) {
         page_bytes_all = 0;
         for (const ListRun& R : e->runs)
           if (e->ll[R.layer].sp.mixer == B2_MIXER_WINDOW_AND_STATE) page_bytes_all += (size_t)c.block_size * (e->ll[R.layer].nk + e->ll[R.layer].nv) * e->esz;
+        page_bytes_all = std::max<size_t>(page_bytes_all, 16);
+      } else if (mixed_arch) {
+        page_bytes_all = 0;
+        for (const ListRun& R : e->runs) {
+          const ListLayer& L = e->ll[R.layer];
+          if (L.sp.mixer == B2_MIXER_MIXED_SCORE_ATTENTION) page_bytes_all += (size_t)c.block_size * (L.nk + L.nv) * e->esz;
+          else if (L.sp.mixer == B2_MIXER_GATED_LATENT) page_bytes_all += (size_t)c.block_size * L.sp.kv_rank * e->esz;
+        }
         page_bytes_all = std::max<size_t>(page_bytes_all, 16);
       } else if (ls) {
         page_bytes_all = 0;
@@ -3163,8 +3796,27 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
             off += (size_t)nb * vb;
           }
         }
+        if (mixed_arch) {
+          for (ListRun& R : e->runs) {
+            const ListLayer& L = e->ll[R.layer];
+            if (L.sp.mixer == B2_MIXER_MIXED_SCORE_ATTENTION) {
+              const size_t kb = (size_t)c.block_size * L.nk * e->esz, vb = (size_t)c.block_size * L.nv * e->esz;
+              R.k_region = (int)e->regions.size();
+              e->regions.push_back({e->l_pool + off, kb});
+              off += (size_t)nb * kb;
+              R.v_region = (int)e->regions.size();
+              e->regions.push_back({e->l_pool + off, vb});
+              off += (size_t)nb * vb;
+            } else if (L.sp.mixer == B2_MIXER_GATED_LATENT) {
+              const size_t pb = (size_t)c.block_size * L.sp.kv_rank * e->esz;
+              R.k_region = (int)e->regions.size();
+              e->regions.push_back({e->l_pool + off, pb});
+              off += (size_t)nb * pb;
+            }
+          }
+        }
         for (ListLayer& L : e->ll) {
-          if (state_arch) break;
+          if (state_arch || mixed_arch) break;
           if (heads_cache) {
             const size_t kb = (size_t)c.block_size * L.nk * e->esz, vb = (size_t)c.block_size * L.nv * e->esz;
             L.cache_region = (int)e->regions.size();
@@ -3182,7 +3834,7 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
           off += (size_t)nb * pb;
         }
         for (ListLayer& L : e->ll)
-          if (!state_arch && !heads_cache && L.sp.kv_from >= 0) L.cache_region = e->ll[L.sp.kv_from].cache_region;
+          if (!state_arch && !mixed_arch && !heads_cache && L.sp.kv_from >= 0) L.cache_region = e->ll[L.sp.kv_from].cache_region;
       } else {
         E_TRY(dalloc(&e->kv_pool, (size_t)2 * c.num_layers * e->layer_kv_elems));
         E_CUDA(cudaMemset(e->kv_pool, 0, (size_t)2 * c.num_layers * e->layer_kv_elems * 2));
@@ -3222,6 +3874,13 @@ extern "C" int b2_engine_load_tensor(b2_engine* e, const char* hf_name, const vo
   return layer_tensor(e, hf_name, host_bf16, nbytes);
 }
 
+extern "C" int b2_engine_load_int_tensor(b2_engine* e, const char* name, const int32_t* host_i32, size_t count) {
+  B2_REQUIRE(e && name && host_i32, "b2_engine_load_int_tensor: null argument");
+  B2_REQUIRE(list_arch(e->cfg.arch), "b2_engine_load_int_tensor: this family has no integer tensors");
+  B2_CUDA_OK(cudaSetDevice(e->device));
+  return list_int_tensor(e, name, host_i32, count);
+}
+
 extern "C" int b2_engine_load_safetensors(b2_engine* e, const char* path) {
   B2_REQUIRE(e && path, "b2_engine_load_safetensors: null argument");
   B2_CUDA_OK(cudaSetDevice(e->device));
@@ -3231,9 +3890,9 @@ extern "C" int b2_engine_load_safetensors(b2_engine* e, const char* path) {
 extern "C" int b2_engine_finalize(b2_engine* e) {
   B2_REQUIRE(e, "b2_engine_finalize: null engine");
   const int arch = e->cfg.arch;
-  if (arch == B2_ARCH_BUMALIX) {
+  if (arch == B2_ARCH_BUMALIX || arch == B2_ARCH_TINEVIK) {
     B2_CUDA_OK(cudaSetDevice(e->device));
-    B2_TRY(state_finalize(e));
+    B2_TRY(arch == B2_ARCH_BUMALIX ? state_finalize(e) : mixed_finalize(e));
     e->finalized = true;
     return 0;
   }
@@ -3287,6 +3946,8 @@ extern "C" void b2_engine_free(b2_engine* e) {
   if (e->h_tok) cudaFreeHost(e->h_tok);
   if (e->ev_tok) cudaEventDestroy(e->ev_tok);
   F(e->partial2); F(e->attn_scratch2); F(e->ssq);
+  if (e->l_head == e->l_embed) e->l_head = nullptr;   // (a tied head is the embedding table)
+  F(e->l_final_bias);
   F(e->l_embed); F(e->l_head); F(e->l_embed_gain); F(e->l_final_gain); F(e->l_pool); F(e->l_h); F(e->l_qd); F(e->l_qrot); F(e->l_qabs);
   F(e->l_xperm); F(e->l_upf); if (e->h_offsets) cudaFreeHost(e->h_offsets);
   F(e->l_q); F(e->l_vfirst); F(e->l_cross); F(e->l_qb); F(e->d_row_seq); F(e->d_row_first); F(e->d_row_end);
@@ -3296,6 +3957,7 @@ extern "C" void b2_engine_free(b2_engine* e) {
     F(L.wqd); F(L.ukT); F(L.uv); F(L.wo); F(L.up); F(L.down); F(L.gain1); F(L.gain2); F(L.lat_gain); F(L.sink); F(L.router); F(L.corr);
     F(L.gain1b); F(L.gain2b); F(L.qkv_bias); F(L.o_bias); F(L.conv_w); F(L.talk); F(L.vmix); F(L.conv_ring);
     F(L.wo2); F(L.sh_up); F(L.sh_down); F(L.qk_gain); F(L.head_gain); F(L.a2); F(L.a2_bias); F(L.g2); F(L.a_log); F(L.out_gain_l); F(L.out_gain_r); F(L.poly);
+    F(L.bias1); F(L.bias1b); F(L.bias2); F(L.bias2b); F(L.latq_gain); F(L.uq); F(L.table);
   }
   for (auto& R : e->runs) {
     F(R.state); F(R.ring);

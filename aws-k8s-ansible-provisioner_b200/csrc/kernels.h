@@ -280,6 +280,17 @@ int launch_branch_add(float* h, const float* a, const float* gain_a, const float
                       const float* gain_next = nullptr, void* x_next = nullptr, int x_f32 = 0);
 // logits <- cap * tanh(logits / cap), in place
 int launch_softcap(float* logits, size_t n, float cap, cudaStream_t s);
+// Layer norms with gain and bias, ln(v) = (v - mean) / sqrt(variance + eps) * w + b, around the same fp32 stream:
+// x[t] = ln(h[rows ? rows[t] : t]), x fp32 or bf16
+int launch_layer_norm(const float* h, const float* w, const float* b, void* x, int x_f32, int T, int W, float eps, const int32_t* rows, cudaStream_t s);
+// h[t] += ln(y[t]): the norm behind a sublayer and the residual add in one pass.  pair_slot != null: the sublayer's output is the sum of the
+// token's routed rows, y[t] = coef * sum_k y[pair_slot[t * top + k]].  With w_next the norm in front of the next sublayer as well.
+int launch_layer_norm_add(float* h, const float* y, const int32_t* pair_slot, int top, float coef, const float* w, const float* b, int T, int W, float eps,
+                          cudaStream_t s, const float* w_next = nullptr, const float* b_next = nullptr, void* x_next = nullptr, int x_f32 = 0);
+// act[i] = softplus(p) z^2 + z / 2 for z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 otherwise; pq (device) = p, q
+int launch_xielu(const float* z, const float* pq, void* act, int act_f32, size_t n, cudaStream_t s);
+// out[t][i] = a[t][i] * sigmoid(gate[t * gate_ld + i]), out fp32 or bf16 [T][N]
+int launch_sigmoid_gate(const float* a, const float* gate, int gate_ld, void* out, int out_f32, int T, int N, cudaStream_t s);
 
 // ---- attn_heads.cu: softmax attention with per-head keys and values, any head width, fp32 or bf16 cache ----
 struct HeadsGeom {
@@ -295,6 +306,11 @@ struct HeadsGeom {
   int cross;                        // 1: every query head's weights are applied to the values of every key/value head (for talk_gate)
   int swizzled;                     // 1: K and V rows go into the page layout of the GQA kernels (bf16, 128 wide, kv_swizzled_chunk) and the
                                     //    queries out as bf16, so that attn_decode.cu / attn_prefill_tc.cu serve the layer
+  // mixers whose scores are mixed over the heads before the softmax (heads_finish_halves / heads_attention_premix)
+  float rot_factor;                 // rotary angles of q and k are divided by this (0 = 1)
+  int rot_values;                   // 1: the value of position j is rotated by j over all of vdim (pairs (m, m + vdim/2), angle j * rot_base^(-2m/vdim))
+                                    //    before it is cached, and a query's weighted sum is turned back by its own position
+  float softcap;                    // scores <- softcap * tanh(scores / softcap) (0 = none)
 };
 // proj [T][ld] fp32 = q | k | v (| more) of the fused projection.  bias [heads*dim + kv_heads*(dim+vdim)] or null; conv_w [channels][taps];
 // ring [sequence slots][taps][channels] fp32 (row = position mod taps); row_seq / row_first / row_end [T]: the token's sequence slot and the first row / one past
@@ -316,6 +332,18 @@ int launch_heads_attention(const float* q, const void* k_cache, const void* v_ca
 // the GQA kernels' page layout and the queries out as bf16 (q_bf16) instead.
 int launch_heads_finish_rownorm(const float* proj, int ld, const HeadsGeom& g, const float* bias, const float* qk_gain, const int32_t* slots,
                                 float* q_out, void* k_cache, void* v_cache, int cache_f32, int T, cudaStream_t s, void* q_bf16 = nullptr);
+// What follows a fused q | k | v projection (proj [T][ld] fp32) when every q and k head is RMS-normed with one gain of `dim` entries
+// (q_gain, k_gain; null = no norm) and then rotated on half-split pairs: entry i of the first rot_dims pairs with entry i + rot_dims/2,
+// angle position * rot_base^(-2i/rot_dims) / rot_factor; with g.rot_values the values are rotated over all of vdim the same way (no factor).
+// Writes q_out [T][heads*dim] fp32 and the token's K and V cache rows (plain layout).
+int launch_heads_finish_halves(const float* proj, int ld, const HeadsGeom& g, const float* q_gain, const float* k_gain, const int32_t* positions,
+                               const int32_t* slots, float* q_out, void* k_cache, void* v_cache, int cache_f32, int T, cudaStream_t s);
+// Softmax attention whose scaled scores pass the cap and are mixed over the heads, s'_a = sum_b mix[a][b] s_b (mix [heads][heads], null =
+// none), BEFORE the softmax; causal, with g.window; with g.rot_values the weighted sum is turned back by the query's position.  All heads of
+// a query token are formed together.  tiles == null: decode form.  out [T][heads*vdim] (fp32 or bf16).
+int launch_heads_attention_premix(const float* q, const void* k_cache, const void* v_cache, int cache_f32, const HeadsGeom& g, const float* mix,
+                                  const int32_t* block_table, int bt_stride, int block_size, const PrefillTile* tiles, int ntiles,
+                                  const int32_t* positions, const int32_t* seq_lens, void* out, int out_f32, int T, cudaStream_t s);
 int launch_talk_gate(const float* cross, const float* talk, const float* gate, int gate_ld, void* out, int out_f32, int heads, int kv_heads,
                      int vdim, int T, cudaStream_t s);
 
@@ -358,14 +386,20 @@ int launch_state_out_gate(const float* o, const float* gain, const float* gate, 
 struct LatentGeom {
   int heads, dim, rot_dim, vdim, kv_rank, rot_dims;
   float rot_base, scale, eps;
+  int window;   // > 0: query i sees key j only when i - j < window (0 = every earlier key)
 };
 // qd [T][ld] fp32 = the fused projection's output: per head [dim | rot_dim], then (has_kv) the latent and the key piece.
 // Writes q_nope [T][heads*dim] (operand type), q_rot [T][heads*rot_dim] fp32 (rotated) and, when has_kv, the token's cache row.
 int launch_latent_finish(const float* qd, int ld, const LatentGeom& g, int has_kv, const float* latent_gain, const int32_t* positions,
                          const int32_t* slots, void* q_nope, int x_f32, float* q_rot, void* cache, int cache_f32, int T, cudaStream_t s);
+// proj [T][ld] fp32 holds a query latent (q_rank entries at column off_q) and the key/value latent (kv_rank entries at off_c): both are
+// RMS-normed with a plain gain; xq [T][q_rank] (operand type) feeds the query up-projection, the other is the token's cache row (a cache
+// without a rotated piece: rows of kv_rank).
+int launch_latent_pair_finish(const float* proj, int ld, int off_q, int q_rank, int off_c, int kv_rank, const float* gain_q, const float* gain_c,
+                              float eps, const int32_t* slots, void* xq, void* cache, int x_f32, int T, cudaStream_t s);
 // scores and weighted latent sum: q_abs [T][heads][kv_rank] fp32 (query pulled through the key up-projection), q_rot as above;
 // tiles == null: decode form (token i is the newest token of block-table row i at positions[i]; seq_lens[i] == 0 rows are empty).
-// out_lat [T][heads][kv_rank] (operand type).
+// out_lat [T][heads][kv_rank] (operand type).  sink [heads] or null (plain softmax).
 int launch_latent_attention(const float* q_abs, const float* q_rot, const void* cache, int cache_f32, const LatentGeom& g,
                             const int32_t* block_table, int bt_stride, int block_size, const PrefillTile* tiles, int ntiles,
                             const int32_t* positions, const int32_t* seq_lens, const float* sink, void* out_lat, int x_f32, int T,
@@ -382,6 +416,8 @@ struct RouteGeom {
 // x [T][W] (operand type), router [experts][W] fp32, correction [experts] fp32 (null = none) -> idx [T][top], weight [T][top]
 int launch_route(const void* x, int x_f32, const float* router, const float* correction, const RouteGeom& g, int32_t* idx, float* weight,
                  int T, int W, cudaStream_t s);
+// no router: idx[t][k] = table[ids[t]][k] (table [vocab][top] int32, entries clamped into [0, experts)), weight[t][k] = 1 / top
+int launch_route_table(const int32_t* ids, const int32_t* table, int vocab, int experts, int top, int32_t* idx, float* weight, int T, cudaStream_t s);
 // counting sort of the T*top (token, choice) pairs by expert: offsets [experts + 1] (the buffer holds 3 * stride ints,
 // stride >= experts + 1: the kernels keep a histogram and a cursor behind the offsets, at offsets + stride and
 // offsets + 2 * stride; zero it once when it is allocated), slot_token [T*top] (slot -> token), pair_slot [T*top] (pair -> slot).

@@ -2,6 +2,7 @@
 // one).  b2serve, the Python mirror and bin/trace_run all choose the model class through this one function, so a family
 // is added to the framework here, in b2_engine_create and nowhere else.  Host code only.
 //
+// The fourth layer-list family, Tinevik, is described above its reader (tinevik_config).
 // HF families are told apart by "model_type" (the keys follow HF's Qwen3Config / Phi3Config / OPTConfig); Lerasun by
 // "architecture": "Lerasun", whose config lists its layers one by one:
 //   {"architecture": "Lerasun", "vocab": V, "width": W, "logit_scale": s, "norm": {"eps": e},
@@ -366,6 +367,138 @@ int bumalix_config(const Value& j, b2_config* c, b2_layer_spec* specs, int max_s
   return 0;
 }
 
+// Tinevik: {"architecture": "Tinevik", "vocab": V, "width": W, "embedding": {"scale": s}?, "logit_scale": s?, "norm": {"eps": e},
+//   "layers": [{"type": "gla", "mixer": {"heads", "dim", "vdim", "tau"}, "mlp": ..., "weights_of": j?},
+//              {"type": "attention", "mixer": {"heads", "kv_heads"?, "dim", "vdim", "scale", "softcap"?,
+//                                              "rot": {"base", "dims", "scaling": {"factor"}?}?}, "mlp": ...},
+//              {"type": "latent_attention", "mixer": {"heads", "dim", "vdim", "kv_rank", "q_rank", "scale", "mask": {"size"}?},
+//               "mlp": null | {"kind": "dense", "ff"} | {"kind": "moe", "expert": {"ff", "limit"}, "router": {"experts", "top"}}}, ...]}
+int tinevik_config(const Value& j, b2_config* c, b2_layer_spec* specs, int max_specs) {
+  c->arch = B2_ARCH_TINEVIK;
+  CFG_TRY(need_int(j, "vocab", "config", &c->vocab));
+  CFG_TRY(need_int(j, "width", "config", &c->hidden));
+  const Value* norm = j.find("norm");
+  if (!norm || !norm->is_object()) {
+    b2_set_error("config.json: norm missing");
+    return -22;
+  }
+  CFG_TRY(need_float(*norm, "eps", "norm", &c->rms_eps));
+  c->norm_groups = 1;
+  c->norm_kind = 1;
+  c->embed_scale = 1.0f;
+  if (const Value* em = j.find("embedding"))
+    if (em->is_object())
+      if (const Value* sc = em->find("scale"))
+        if (sc->is_number()) c->embed_scale = (float)sc->as_double();
+  c->logit_scale = 1.0f;
+  if (const Value* ls = j.find("logit_scale"))
+    if (ls->is_number()) c->logit_scale = (float)ls->as_double();
+  const Value* layers = j.find("layers");
+  if (!layers || !layers->is_array() || layers->size() == 0) {
+    b2_set_error("config.json: layers missing or empty");
+    return -22;
+  }
+  c->num_layers = (int)layers->size();
+  if (c->num_layers > max_specs || specs == nullptr) {
+    b2_set_error("config.json: %d layers, room for %d layer specs", c->num_layers, max_specs);
+    return -22;
+  }
+  for (int i = 0; i < c->num_layers; ++i) {
+    const Value& L = layers->at(i);
+    b2_layer_spec& s = specs[i];
+    memset(&s, 0, sizeof s);
+    s.kv_from = -1;
+    s.weights_of = -1;
+    char where[64];
+    snprintf(where, sizeof where, "layers[%d].mixer", i);
+    const Value* type = L.find("type");
+    const Value* m = L.find("mixer");
+    if (!type || !type->is_string() || !m || !m->is_object()) {
+      b2_set_error("config.json: layers[%d] needs type and mixer", i);
+      return -22;
+    }
+    if (const Value* wo = L.find("weights_of"))
+      if (wo->is_number()) {
+        s.weights_of = (int)wo->as_int();
+        if (s.weights_of < 0 || s.weights_of >= c->num_layers || s.weights_of == i) {
+          b2_set_error("config.json: layers[%d].weights_of %d names no other layer", i, s.weights_of);
+          return -22;
+        }
+      }
+    const std::string ty = type->as_string();
+    CFG_TRY(need_int(*m, "heads", where, &s.heads));
+    s.kv_heads = s.heads;
+    CFG_TRY(need_int(*m, "dim", where, &s.dim));
+    CFG_TRY(need_int(*m, "vdim", where, &s.vdim));
+    if (ty == "gla") {
+      s.mixer = B2_MIXER_DECAY_STATE;
+      CFG_TRY(need_float(*m, "tau", where, &s.s_tau));
+      s.s_heads = s.heads;
+      s.s_dim = s.dim;
+      s.s_vdim = s.vdim;
+    } else if (ty == "attention") {
+      s.mixer = B2_MIXER_MIXED_SCORE_ATTENTION;
+      if (const Value* kh = m->find("kv_heads"))
+        if (kh->is_number()) s.kv_heads = (int)kh->as_int();
+      CFG_TRY(need_float(*m, "scale", where, &s.scale));
+      if (const Value* cap = m->find("softcap"))
+        if (cap->is_number()) s.softcap = (float)cap->as_double();
+      s.score_mix = 1;
+      s.rot_factor = 1.0f;
+      const Value* rot = m->find("rot");
+      if (rot && rot->is_object()) {  // no "rot": nothing is rotated, values included
+        CFG_TRY(need_float(*rot, "base", where, &s.rot_base));
+        CFG_TRY(need_int(*rot, "dims", where, &s.rot_dims));
+        s.rot_values = 1;
+        if (const Value* sc = rot->find("scaling"))
+          if (sc->is_object()) CFG_TRY(need_float(*sc, "factor", where, &s.rot_factor));
+      }
+    } else if (ty == "latent_attention") {
+      s.mixer = B2_MIXER_GATED_LATENT;
+      CFG_TRY(need_int(*m, "kv_rank", where, &s.kv_rank));
+      CFG_TRY(need_int(*m, "q_rank", where, &s.q_rank));
+      CFG_TRY(need_float(*m, "scale", where, &s.scale));
+      const Value* mask = m->find("mask");
+      if (mask && mask->is_object()) CFG_TRY(need_int(*mask, "size", where, &s.window));  // no "mask": every earlier key is seen
+    } else {
+      b2_set_error("config.json: layers[%d]: mixer type '%s' not built (gla, attention, latent_attention)", i, ty.c_str());
+      return -22;
+    }
+    const Value* mlp = L.find("mlp");
+    s.ff = B2_FF_NONE;
+    if (mlp && mlp->is_object()) {
+      snprintf(where, sizeof where, "layers[%d].mlp", i);
+      const Value* kind = mlp->find("kind");
+      const std::string kd = kind && kind->is_string() ? kind->as_string() : "?";
+      if (kd == "dense") {
+        s.ff = B2_FF_XIELU;
+        CFG_TRY(need_int(*mlp, "ff", where, &s.ff_dim));
+      } else if (kd == "moe") {
+        s.ff = B2_FF_TABLE_EXPERTS;
+        const Value* ex = mlp->find("expert");
+        const Value* ro = mlp->find("router");
+        if (!ex || !ex->is_object() || !ro || !ro->is_object()) {
+          b2_set_error("config.json: %s needs expert and router", where);
+          return -22;
+        }
+        CFG_TRY(need_int(*ex, "ff", where, &s.ff_dim));
+        CFG_TRY(need_float(*ex, "limit", where, &s.ff_limit));
+        CFG_TRY(need_int(*ro, "experts", where, &s.experts));
+        CFG_TRY(need_int(*ro, "top", where, &s.top));
+        s.groups = s.groups_keep = 1;
+      } else {
+        b2_set_error("config.json: %s.kind '%s' not built (dense, moe)", where, kd.c_str());
+        return -22;
+      }
+    }
+  }
+  c->layer_specs = specs;
+  c->tie_embeddings = 1;
+  c->num_q_heads = c->num_kv_heads = 0;
+  c->head_dim = c->intermediate = 0;
+  return 0;
+}
+
 }  // namespace
 
 extern "C" int b2_config_from_dir(const char* model_dir, b2_config* c, b2_layer_spec* specs, int32_t max_specs) {
@@ -392,11 +525,13 @@ extern "C" int b2_config_from_dir(const char* model_dir, b2_config* c, b2_layer_
   c->norm_groups = 0;
   c->loop_start = c->loop_stop = c->loop_times = 0;
   c->logit_softcap = 0.f;
+  c->norm_kind = 0;
   const Value* archv = j.find("architecture");
   if (archv && archv->is_string()) {
     if (archv->as_string() == "Lerasun") return lerasun_config(j, c, specs, max_specs);
     if (archv->as_string() == "Kedasun") return kedasun_config(j, c, specs, max_specs);
     if (archv->as_string() == "Bumalix") return bumalix_config(j, c, specs, max_specs);
+    if (archv->as_string() == "Tinevik") return tinevik_config(j, c, specs, max_specs);
     b2_set_error("%s: architecture '%s' not built", path.c_str(), archv->as_string().c_str());
     return -22;
   }

@@ -219,6 +219,22 @@ __global__ void __launch_bounds__(256) route_slot_weights_kernel(const float* __
   if (p < npairs) slot_weight[pair_slot[p]] = weight[p];
 }
 
+// No router: a table row per token id names the token's experts, each weighted 1 / top.  idx [T][top], weight [T][top].
+__global__ void __launch_bounds__(256) route_table_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ table, int vocab, int experts,
+                                                          int top, int32_t* __restrict__ idx, float* __restrict__ weight, int npairs) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int p = blockIdx.x * 256 + threadIdx.x;
+  if (p >= npairs) return;
+  const int t = p / top, k = p - t * top;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  int x = table[(size_t)id * top + k];
+  x = x < 0 ? 0 : (x >= experts ? experts - 1 : x);
+  idx[p] = x;
+  weight[p] = 1.0f / (float)top;
+}
+
 // act = bf16(max(up, 0)^2): the experts' activation between the two dense products of a prompt-sized step
 __global__ void __launch_bounds__(256) relu2_round_kernel(const float4* __restrict__ up, uint2* __restrict__ act, size_t n4) {
   pdl_wait();
@@ -278,6 +294,13 @@ int launch_route_permute(const int32_t* idx, int T, int top, int experts, int32_
   B2_CUDA_OK(b2_launch(route_count_kernel, dim3((npairs + 255) / 256), dim3(256), (size_t)experts * sizeof(int), s, idx, npairs, experts, counts));
   B2_CUDA_OK(b2_launch(route_scan_kernel, dim3(1), dim3(32), 0, s, counts, experts, offsets, cursor));
   B2_CUDA_OK(b2_launch(route_place_kernel, dim3((npairs + 255) / 256), dim3(256), 0, s, idx, npairs, top, cursor, slot_token, pair_slot));
+  return 0;
+}
+
+int launch_route_table(const int32_t* ids, const int32_t* table, int vocab, int experts, int top, int32_t* idx, float* weight, int T, cudaStream_t s) {
+  if (T <= 0) return 0;
+  const int npairs = T * top;
+  B2_CUDA_OK(b2_launch(route_table_kernel, dim3((npairs + 255) / 256), dim3(256), 0, s, ids, table, vocab, experts, top, idx, weight, npairs));
   return 0;
 }
 

@@ -360,6 +360,109 @@ __global__ void __launch_bounds__(256) softcap_kernel(float* __restrict__ logits
   for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) logits[i] = cap * tanhf(logits[i] / cap);
 }
 
+// ---- layer norms with gain and bias in front of and behind every sublayer (Tinevik) ----
+// (x - mean) / sqrt(variance + eps) * w + b, the variance as the mean of the squared deviations (two passes over a row staged in shared
+// memory).  One CTA of 128 threads per row, any width.
+template <typename TX>
+__global__ void __launch_bounds__(128) layer_norm_kernel(const float* __restrict__ h, const float* __restrict__ w, const float* __restrict__ b,
+                                                         TX* __restrict__ x, int W, float eps, const int32_t* __restrict__ rows) {
+  extern __shared__ float lrow[];
+  __shared__ float red[4];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const float* src = h + (size_t)(rows ? rows[t] : t) * W;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < W; i += 128) {
+    const float v = src[i];
+    lrow[i] = v;
+    s += v;
+  }
+  const float mean = block_sum_128(s, red) / (float)W;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += 128) {
+    const float d = lrow[i] - mean;
+    q = fmaf(d, d, q);
+  }
+  const float r = 1.0f / sqrtf(block_sum_128(q, red) / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += 128) x[(size_t)t * W + i] = (TX)((lrow[i] - mean) * r * w[i] + b[i]);
+}
+
+// h[t] += ln(y[t]) (gain w, bias b); with pair_slot the sublayer's output is the sum of the token's `top` routed rows times coef,
+// y[t] = coef * sum_k y[pair_slot[t * top + k]].  With w_next the norm in front of the next sublayer follows, x_next[t] = ln(h[t]).
+template <typename TX>
+__global__ void __launch_bounds__(128) layer_norm_add_kernel(float* __restrict__ h, const float* __restrict__ y, const int32_t* __restrict__ pair_slot,
+                                                             int top, float coef, const float* __restrict__ w, const float* __restrict__ b, int W,
+                                                             float eps, const float* __restrict__ w_next, const float* __restrict__ b_next,
+                                                             TX* __restrict__ x_next) {
+  extern __shared__ float lrow[];
+  __shared__ float red[4];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < W; i += 128) {
+    float v;
+    if (pair_slot != nullptr) {
+      v = 0.f;
+      for (int k = 0; k < top; ++k) v += y[(size_t)pair_slot[t * top + k] * W + i];
+      v *= coef;
+    } else {
+      v = y[(size_t)t * W + i];
+    }
+    lrow[i] = v;
+    s += v;
+  }
+  const float mean = block_sum_128(s, red) / (float)W;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += 128) {
+    const float d = lrow[i] - mean;
+    q = fmaf(d, d, q);
+  }
+  const float r = 1.0f / sqrtf(block_sum_128(q, red) / (float)W + eps);
+  float s2 = 0.f;
+  for (int i = threadIdx.x; i < W; i += 128) {
+    const float hn = h[(size_t)t * W + i] + ((lrow[i] - mean) * r * w[i] + b[i]);
+    h[(size_t)t * W + i] = hn;
+    lrow[i] = hn;   // (each thread re-reads only what it wrote)
+    s2 += hn;
+  }
+  if (w_next == nullptr) return;
+  const float mean2 = block_sum_128(s2, red) / (float)W;
+  float q2 = 0.f;
+  for (int i = threadIdx.x; i < W; i += 128) {
+    const float d = lrow[i] - mean2;
+    q2 = fmaf(d, d, q2);
+  }
+  const float r2 = 1.0f / sqrtf(block_sum_128(q2, red) / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += 128) x_next[(size_t)t * W + i] = (TX)((lrow[i] - mean2) * r2 * w_next[i] + b_next[i]);
+}
+
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// act = a(z), a(z) = softplus(p) z^2 + z / 2 for z > 0 and (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 otherwise; pq (device) = p, q
+template <typename TX>
+__global__ void __launch_bounds__(256) xielu_kernel(const float* __restrict__ z, const float* __restrict__ pq, TX* __restrict__ act, size_t n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const float ap = softplus_f(pq[0]), an = 0.5f + softplus_f(pq[1]);
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) {
+    const float v = z[i];
+    act[i] = (TX)(v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(an, expm1f(v) - v, 0.5f * v));
+  }
+}
+
+// out[t][i] = a[t][i] * sigmoid(gate[t * gate_ld + i])
+template <typename TX>
+__global__ void __launch_bounds__(256) sigmoid_gate_kernel(const float* __restrict__ a, const float* __restrict__ gate, int gate_ld, TX* __restrict__ out,
+                                                           int N) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  for (int i = blockIdx.y * 256 + threadIdx.x; i < N; i += 256 * gridDim.y)
+    out[(size_t)t * N + i] = (TX)(a[(size_t)t * N + i] / (1.0f + expf(-gate[(size_t)t * gate_ld + i])));
+}
+
 }  // namespace
 
 constexpr int GN_EARLY_ROWS = 1024;
@@ -476,6 +579,56 @@ int launch_softcap(float* logits, size_t n, float cap, cudaStream_t s) {
   if (n == 0 || !(cap > 0.f)) return 0;
   const unsigned blocks = (unsigned)std::min<size_t>((n + 255) / 256, 4096);
   B2_CUDA_OK(b2_launch(softcap_kernel, dim3(blocks), dim3(256), 0, s, logits, n, cap));
+  return 0;
+}
+
+int launch_layer_norm(const float* h, const float* w, const float* b, void* x, int x_f32, int T, int W, float eps, const int32_t* rows, cudaStream_t s) {
+  if (T <= 0) return 0;
+  B2_REQUIRE((size_t)W * 4 <= 160 * 1024, "layer_norm: a row of %d numbers does not fit in shared memory", W);
+  const size_t smem = (size_t)W * 4;
+  if (x_f32) {
+    static B2PerDeviceOnce once;
+    if (smem > 48 * 1024) b2_prefer_max_smem(layer_norm_kernel<float>, once);
+    B2_CUDA_OK(b2_launch(layer_norm_kernel<float>, dim3(T), dim3(128), smem, s, h, w, b, (float*)x, W, eps, rows));
+  } else {
+    static B2PerDeviceOnce once;
+    if (smem > 48 * 1024) b2_prefer_max_smem(layer_norm_kernel<bf16>, once);
+    B2_CUDA_OK(b2_launch(layer_norm_kernel<bf16>, dim3(T), dim3(128), smem, s, h, w, b, (bf16*)x, W, eps, rows));
+  }
+  return 0;
+}
+
+int launch_layer_norm_add(float* h, const float* y, const int32_t* pair_slot, int top, float coef, const float* w, const float* b, int T, int W, float eps,
+                          cudaStream_t s, const float* w_next, const float* b_next, void* x_next, int x_f32) {
+  if (T <= 0) return 0;
+  B2_REQUIRE((size_t)W * 4 <= 160 * 1024, "layer_norm_add: a row of %d numbers does not fit in shared memory", W);
+  B2_REQUIRE((w_next == nullptr) == (x_next == nullptr) && (w_next == nullptr) == (b_next == nullptr), "layer_norm_add: the following norm needs gain, bias and output");
+  const size_t smem = (size_t)W * 4;
+  if (x_f32 || x_next == nullptr) {
+    static B2PerDeviceOnce once;
+    if (smem > 48 * 1024) b2_prefer_max_smem(layer_norm_add_kernel<float>, once);
+    B2_CUDA_OK(b2_launch(layer_norm_add_kernel<float>, dim3(T), dim3(128), smem, s, h, y, pair_slot, top, coef, w, b, W, eps, w_next, b_next, (float*)x_next));
+  } else {
+    static B2PerDeviceOnce once;
+    if (smem > 48 * 1024) b2_prefer_max_smem(layer_norm_add_kernel<bf16>, once);
+    B2_CUDA_OK(b2_launch(layer_norm_add_kernel<bf16>, dim3(T), dim3(128), smem, s, h, y, pair_slot, top, coef, w, b, W, eps, w_next, b_next, (bf16*)x_next));
+  }
+  return 0;
+}
+
+int launch_xielu(const float* z, const float* pq, void* act, int act_f32, size_t n, cudaStream_t s) {
+  if (n == 0) return 0;
+  const int blocks = (int)std::min<size_t>((n + 255) / 256, 148 * 16);
+  if (act_f32) B2_CUDA_OK(b2_launch(xielu_kernel<float>, dim3(blocks), dim3(256), 0, s, z, pq, (float*)act, n));
+  else B2_CUDA_OK(b2_launch(xielu_kernel<bf16>, dim3(blocks), dim3(256), 0, s, z, pq, (bf16*)act, n));
+  return 0;
+}
+
+int launch_sigmoid_gate(const float* a, const float* gate, int gate_ld, void* out, int out_f32, int T, int N, cudaStream_t s) {
+  if (T <= 0) return 0;
+  const dim3 grid(T, T >= 1024 ? 1 : std::max(1, std::min((N + 255) / 256, 1024 / T)));
+  if (out_f32) B2_CUDA_OK(b2_launch(sigmoid_gate_kernel<float>, grid, dim3(256), 0, s, a, gate, gate_ld, (float*)out, N));
+  else B2_CUDA_OK(b2_launch(sigmoid_gate_kernel<bf16>, grid, dim3(256), 0, s, a, gate, gate_ld, (bf16*)out, N));
   return 0;
 }
 

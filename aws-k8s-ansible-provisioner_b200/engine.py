@@ -37,7 +37,7 @@ class EngineConfig:
     max_seqs: int = 64
     max_batch_tokens: int = 8192
     use_cuda_graphs: bool = True
-    arch: str = "qwen3"          # "qwen3" | "phi3" | "opt" | "lerasun" | "kedasun" | "bumalix" (include/b2_engine.h, enum b2_arch)
+    arch: str = "qwen3"          # "qwen3" | "phi3" | "opt" | "lerasun" | "kedasun" | "bumalix" | "tinevik" (include/b2_engine.h, enum b2_arch)
     rotary_dim: int = 0          # 0 = head_dim
     max_positions: int = 0       # OPT: learned position table rows - 2 (0 = max_model_len)
     sliding_window: int = 0      # Phi-3: attend to the last N keys only (0 = all)
@@ -48,6 +48,7 @@ class EngineConfig:
     norm_groups: int = 0         # Kedasun: pieces of every norm (0 = 1)
     loop: tuple = (0, 0, 0)      # Bumalix: layers [start, stop) run `times` times in a row (times 0 = no loop)
     logit_softcap: float = 0.0   # logits <- cap * tanh(logits / cap) (0 = none)
+    norm_kind: int = 0           # 1: layer norms with gain and bias around every sublayer (Tinevik)
 
     @staticmethod
     def lerasun(model_cfg: dict, **runtime) -> "EngineConfig":
@@ -75,6 +76,14 @@ class EngineConfig:
                             arch="bumalix", layers=model_cfg["layers"], tie_embeddings=False, num_q_heads=0, num_kv_heads=0, head_dim=0,
                             intermediate=0, loop=(int(lp.get("start", 0)), int(lp.get("stop", 0)), int(lp.get("times", 0))),
                             logit_softcap=float(model_cfg.get("logit_softcap") or 0.0), **runtime)
+
+    @staticmethod
+    def tinevik(model_cfg: dict, **runtime) -> "EngineConfig":
+        """From the dict a Tinevik config.json holds (width, vocab, embedding.scale, logit_scale, norm.eps, layers) plus runtime sizing."""
+        return EngineConfig(num_layers=len(model_cfg["layers"]), hidden=model_cfg["width"], vocab=model_cfg["vocab"],
+                            rms_eps=model_cfg["norm"]["eps"], embed_scale=(model_cfg.get("embedding") or {}).get("scale", 1.0),
+                            logit_scale=model_cfg.get("logit_scale", 1.0), arch="tinevik", layers=model_cfg["layers"], tie_embeddings=True,
+                            num_q_heads=0, num_kv_heads=0, head_dim=0, intermediate=0, norm_kind=1, **runtime)
 
     def kv_bytes_per_token(self) -> int:
         return 2 * self.num_layers * self.num_kv_heads * self.head_dim * 2
@@ -114,7 +123,8 @@ class Engine:
         c.rope_theta = cfg.rope_theta
         c.gpu_mem_fraction = cfg.gpu_mem_fraction
         c.arch = {"qwen3": capi.ARCH_QWEN3, "phi3": capi.ARCH_PHI3, "opt": capi.ARCH_OPT, "lerasun": capi.ARCH_LERASUN,
-                  "kedasun": capi.ARCH_KEDASUN, "bumalix": capi.ARCH_BUMALIX}[cfg.arch]
+                  "kedasun": capi.ARCH_KEDASUN, "bumalix": capi.ARCH_BUMALIX, "tinevik": capi.ARCH_TINEVIK}[cfg.arch]
+        c.norm_kind = int(cfg.norm_kind)
         c.loop_start, c.loop_stop, c.loop_times = (int(v) for v in cfg.loop)
         c.logit_softcap = float(cfg.logit_softcap)
         c.compute_f32 = int(cfg.compute_f32)
@@ -125,7 +135,7 @@ class Engine:
         if cfg.layers is not None:
             self._specs = (b2_layer_spec * len(cfg.layers))()
             for sp, layer in zip(self._specs, cfg.layers):
-                _fill_layer_spec(sp, layer)
+                _fill_layer_spec(sp, dict(layer, _tinevik=True) if cfg.arch == "tinevik" else layer)
             c.layer_specs = self._specs
         c.rotary_dim = int(cfg.rotary_dim)
         c.max_positions = int(cfg.max_positions)
@@ -152,9 +162,9 @@ class Engine:
         specs = (b2_layer_spec * 1024)()
         check(lib.b2_config_from_dir(model_dir.encode(), C.byref(c), specs, 1024), lib)
         arch = {capi.ARCH_QWEN3: "qwen3", capi.ARCH_PHI3: "phi3", capi.ARCH_OPT: "opt", capi.ARCH_LERASUN: "lerasun",
-                capi.ARCH_KEDASUN: "kedasun", capi.ARCH_BUMALIX: "bumalix"}[c.arch]
+                capi.ARCH_KEDASUN: "kedasun", capi.ARCH_BUMALIX: "bumalix", capi.ARCH_TINEVIK: "tinevik"}[c.arch]
         layers = None
-        if arch in ("lerasun", "kedasun", "bumalix"):
+        if arch in ("lerasun", "kedasun", "bumalix", "tinevik"):
             layers = [_layer_dict(specs[i]) for i in range(c.num_layers)]
         cfg = EngineConfig(num_layers=c.num_layers, hidden=c.hidden, num_q_heads=c.num_q_heads, num_kv_heads=c.num_kv_heads,
                            head_dim=c.head_dim, intermediate=c.intermediate, vocab=c.vocab, tie_embeddings=bool(c.tie_embeddings),
@@ -162,7 +172,7 @@ class Engine:
                            max_positions=c.max_positions, sliding_window=c.sliding_window, layers=layers,
                            compute_f32=(dtype == "float32"), logit_scale=c.logit_scale, embed_scale=c.embed_scale,
                            norm_groups=c.norm_groups, loop=(c.loop_start, c.loop_stop, c.loop_times), logit_softcap=c.logit_softcap,
-                           **runtime)
+                           norm_kind=c.norm_kind, **runtime)
         return cls(cfg, device=device, safetensors_path=os.path.join(model_dir, "model.safetensors"))
 
     # ---- weights -----------------------------------------------------------------------
@@ -178,6 +188,11 @@ class Engine:
 
         for name, t in sd.items():
             if "rotary_emb" in name:
+                continue
+            if t.dtype in (torch.int32, torch.int64):   # integer tables
+                t = t.detach().to(torch.int32).contiguous().cpu()
+                check(self.lib.b2_engine_load_int_tensor(self.h, name.encode(), C.cast(C.c_void_p(t.data_ptr()), C.POINTER(C.c_int32)), t.numel()),
+                      self.lib)
                 continue
             t = t.detach().to(torch.bfloat16).contiguous().cpu()
             check(self.lib.b2_engine_load_tensor(self.h, name.encode(), C.c_void_p(t.data_ptr()), t.numel() * 2), self.lib)
@@ -334,6 +349,8 @@ class Engine:
 
 def _fill_layer_spec(sp, layer: dict) -> None:
     """One "layers" entry of a layer-list config.json -> b2_layer_spec (the C registry does the same for a directory)."""
+    if layer["type"] == "gla" or layer["mixer"].get("q_rank") is not None or (layer["type"] == "attention" and layer.get("_tinevik")):
+        return _fill_mixed_spec(sp, layer)
     if layer["type"] in ("attention", "attention_2"):
         return _fill_heads_spec(sp, layer)
     if layer["type"] in ("parallel", "channel_delta"):
@@ -355,6 +372,66 @@ def _fill_layer_spec(sp, layer: dict) -> None:
         g = r.get("groups") or {"count": 1, "keep": 1}
         sp.ff, sp.ff_dim, sp.experts, sp.top = capi.FF_ROUTED_EXPERTS, int(mlp["expert"]["ff"]), int(r["experts"]), int(r["top"])
         sp.groups, sp.groups_keep = int(g["count"]), int(g["keep"])
+
+
+def _fill_mixed_spec(sp, layer: dict) -> None:
+    """Tinevik: "gla", "attention" (scores mixed over the heads before the softmax, rotated values) and "latent_attention" (query latent,
+    window, output gate).  An "attention" entry of this family is marked with "_tinevik": True (Engine.__init__ does it for arch "tinevik")."""
+    m = layer["mixer"]
+    sp.kv_from = -1
+    sp.weights_of = int(layer["weights_of"]) if layer.get("weights_of") is not None else -1
+    sp.heads, sp.dim, sp.vdim = int(m["heads"]), int(m["dim"]), int(m["vdim"])
+    sp.kv_heads = sp.heads
+    if layer["type"] == "gla":
+        sp.mixer, sp.s_tau = capi.MIXER_DECAY_STATE, float(m["tau"])
+        sp.s_heads, sp.s_dim, sp.s_vdim = sp.heads, sp.dim, sp.vdim
+    elif layer["type"] == "attention":
+        sp.mixer = capi.MIXER_MIXED_SCORE_ATTENTION
+        sp.kv_heads = int(m.get("kv_heads", m["heads"]))
+        sp.scale, sp.softcap, sp.score_mix, sp.rot_factor = float(m["scale"]), float(m.get("softcap") or 0.0), 1, 1.0
+        rot = m.get("rot")
+        if rot:
+            sp.rot_base, sp.rot_dims, sp.rot_values = float(rot["base"]), int(rot["dims"]), 1
+            if rot.get("scaling"):
+                sp.rot_factor = float(rot["scaling"]["factor"])
+    else:
+        sp.mixer = capi.MIXER_GATED_LATENT
+        sp.kv_rank, sp.q_rank, sp.scale = int(m["kv_rank"]), int(m["q_rank"]), float(m["scale"])
+        sp.window = int(m["mask"]["size"]) if m.get("mask") else 0
+    mlp = layer.get("mlp")
+    sp.ff = capi.FF_NONE
+    if mlp is not None:
+        if mlp["kind"] == "dense":
+            sp.ff, sp.ff_dim = capi.FF_XIELU, int(mlp["ff"])
+        elif mlp["kind"] == "moe":
+            sp.ff, sp.ff_dim, sp.ff_limit = capi.FF_TABLE_EXPERTS, int(mlp["expert"]["ff"]), float(mlp["expert"]["limit"])
+            sp.experts, sp.top, sp.groups, sp.groups_keep = int(mlp["router"]["experts"]), int(mlp["router"]["top"]), 1, 1
+        else:
+            raise B2Error("feed-forward kind %r not built" % mlp["kind"])
+
+
+def _mixed_layer_dict(sp) -> dict:
+    if sp.mixer == capi.MIXER_DECAY_STATE:
+        ty, m = "gla", {"heads": sp.heads, "dim": sp.dim, "vdim": sp.vdim, "tau": sp.s_tau}
+    elif sp.mixer == capi.MIXER_MIXED_SCORE_ATTENTION:
+        ty, m = "attention", {"heads": sp.heads, "kv_heads": sp.kv_heads, "dim": sp.dim, "vdim": sp.vdim, "scale": sp.scale}
+        if sp.softcap > 0:
+            m["softcap"] = sp.softcap
+        if sp.rot_values:
+            m["rot"] = {"base": sp.rot_base, "dims": sp.rot_dims, "scaling": {"factor": sp.rot_factor}}
+    else:
+        ty, m = "latent_attention", {"heads": sp.heads, "dim": sp.dim, "vdim": sp.vdim, "kv_rank": sp.kv_rank, "q_rank": sp.q_rank, "scale": sp.scale}
+        if sp.window > 0:
+            m["mask"] = {"size": sp.window}
+    mlp = None
+    if sp.ff == capi.FF_XIELU:
+        mlp = {"kind": "dense", "ff": sp.ff_dim}
+    elif sp.ff == capi.FF_TABLE_EXPERTS:
+        mlp = {"kind": "moe", "expert": {"ff": sp.ff_dim, "limit": sp.ff_limit}, "router": {"experts": sp.experts, "top": sp.top}}
+    d = {"type": ty, "mixer": m, "mlp": mlp, "_tinevik": True}
+    if sp.weights_of >= 0:
+        d["weights_of"] = sp.weights_of
+    return d
 
 
 def _fill_state_spec(sp, layer: dict) -> None:
@@ -410,6 +487,8 @@ def _fill_heads_spec(sp, layer: dict) -> None:
 
 
 def _layer_dict(sp) -> dict:
+    if sp.mixer in (capi.MIXER_DECAY_STATE, capi.MIXER_MIXED_SCORE_ATTENTION, capi.MIXER_GATED_LATENT):
+        return _mixed_layer_dict(sp)
     if sp.mixer in (capi.MIXER_WINDOW_AND_STATE, capi.MIXER_DELTA_STATE):
         if sp.mixer == capi.MIXER_WINDOW_AND_STATE:
             left = {"heads": sp.heads, "kv_heads": sp.kv_heads, "dim": sp.dim, "vdim": sp.vdim, "scale": sp.scale}

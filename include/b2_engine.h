@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define B2_ABI_VERSION 5
+#define B2_ABI_VERSION 6
 
 typedef struct b2_engine b2_engine;
 
@@ -43,16 +43,27 @@ enum b2_mixer_kind {
                                     (Bumalix "parallel"): grouped-query softmax attention with biased projections, whole-row RMS norms of q
                                     and k, no positions, a sliding window; and gated linear attention, a matrix state per head with a decay
                                     per key channel (s_heads, s_dim, s_vdim, s_tau) */
-  B2_MIXER_DELTA_STATE = 5       /* gated delta rule: a matrix state per head, short causal convolutions on q / k / v, unit-vector q and k,
+  B2_MIXER_DELTA_STATE = 5,      /* gated delta rule: a matrix state per head, short causal convolutions on q / k / v, unit-vector q and k,
                                     a decay per head and key channel, a step size per head, a low-rank output gate (Bumalix "channel_delta") */
+  B2_MIXER_DECAY_STATE = 6,      /* gated linear attention alone: a matrix state per head with a decay per key channel sigmoid(.)^(1 / s_tau)
+                                    (heads, dim, vdim, s_tau), per-head RMS norm of the read-out, a silu gate (Tinevik "gla") */
+  B2_MIXER_MIXED_SCORE_ATTENTION = 7, /* grouped-query softmax attention whose scores pass a cap and a heads x heads mixing BEFORE the softmax;
+                                    q and k heads RMS-normed with one gain per entry of a head; rotary positions on half-split pairs
+                                    (i, i + rot_dims/2) with the angles divided by rot_factor; values rotated by their own position over
+                                    all of vdim and the weighted sum turned back by the query's (Tinevik "attention") */
+  B2_MIXER_GATED_LATENT = 8      /* attention over a per-token latent with no rotated piece: the query itself goes through a normed latent of
+                                    q_rank entries, a sliding window, a sigmoid gate on the concatenated heads (Tinevik "latent_attention") */
 };
 enum b2_ff_kind {
   B2_FF_NONE = 0,
   B2_FF_ROUTED_EXPERTS = 1,
   B2_FF_CLAMPED_GATED = 2,       /* y = g sigmoid(1.702 g) (u + 1), g = min(W_g x, limit), u = clamp(W_u x, -limit, limit); out = W_d y */
   B2_FF_POLYNORM = 3,            /* W_d p(W_u x), p(z) = a N(z) + b N(z^2) + c N(z^3) + e, N = division by the root mean square over the ff values */
-  B2_FF_SCALED_GATED_EXPERTS = 4 /* sigmoid router, the `top` largest scores; expert = W_d (silu(W_g y) * (W_u y)) on y = score * x (scores not
+  B2_FF_SCALED_GATED_EXPERTS = 4,/* sigmoid router, the `top` largest scores; expert = W_d (silu(W_g y) * (W_u y)) on y = score * x (scores not
                                     renormalised); a shared expert of the same form (shared_ff) on x itself is added */
+  B2_FF_XIELU = 5,               /* W_d a(W_u x), a(z) = softplus(p) z^2 + z / 2 for z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 otherwise */
+  B2_FF_TABLE_EXPERTS = 6        /* experts of the B2_FF_CLAMPED_GATED form; an integer table row per token id names the token's `top` experts,
+                                    each weighted 1 / top (no router) */
 };
 typedef struct b2_layer_spec {
   int32_t mixer;        /* b2_mixer_kind */
@@ -86,6 +97,13 @@ typedef struct b2_layer_spec {
   int32_t s_vdim;       /* its value width per head */
   float   s_tau;        /* its decay is sigmoid(.)^(1 / s_tau) */
   int32_t shared_ff;    /* B2_FF_SCALED_GATED_EXPERTS: inner width of the shared expert (0 = none) */
+  /* ABI 6 */
+  int32_t weights_of;   /* -1: the layer has tensors of its own; j >= 0: it runs with layer j's tensors and a cache / state of its own */
+  int32_t q_rank;       /* B2_MIXER_GATED_LATENT: width of the normed latent the queries are rebuilt from */
+  float   rot_factor;   /* rotary angles of q and k are divided by this (0 = 1) */
+  float   softcap;      /* scores <- softcap * tanh(scores / softcap) before the softmax (0 = none) */
+  int32_t score_mix;    /* 1: the heads' capped scores are mixed by a heads x heads matrix before the softmax */
+  int32_t rot_values;   /* 1: values are rotated by their position over all of vdim and the output turned back */
 } b2_layer_spec;
 
 /* Architecture + runtime sizing.  Field meanings follow HF Qwen3Config
@@ -129,6 +147,9 @@ typedef struct b2_config {
   int32_t loop_stop;         /* state of its own; in front of every pass the stream becomes W_in [x; x0], x0 the embedding output */
   int32_t loop_times;        /* 0 = no loop (and no W_in) */
   float   logit_softcap;     /* logits <- cap * tanh(logits / cap) (0 = none) */
+  /* ABI 6 */
+  int32_t norm_kind;         /* layer-list families: 0 = RMS norms as the family defines them; 1 = layer norms with gain and bias
+                                ((x - mean) / sqrt(variance + eps) * w + b), in front of and behind every sublayer and at the end */
 } b2_config;
 
 /* Model families.  QWEN3: HF:models/qwen3/modeling_qwen3.py (QK-norm, separate q/k/v and gate/up
@@ -156,11 +177,17 @@ typedef struct b2_config {
  * loop.in, l<i>.norm1, l<i>.mix.left.{q,k,v (+ .b), q.norm, k.norm, o, out}, l<i>.mix.right.{q,k,v,g,o,norm,a1,a2,a2.b,out},
  * l<i>.mix.{q,k,v (+ .conv), b, A_log, a1, a2, dt_bias, g1, g2, norm, o}, l<i>.mlp.{up,down,act} or l<i>.mlp.{router, e<k>.{gate,up,down},
  * shared.{gate,up,down}}, final.norm, head.  The low-rank widths (a1, g1) are taken from the tensors. */
-enum b2_arch { B2_ARCH_QWEN3 = 0, B2_ARCH_PHI3 = 1, B2_ARCH_OPT = 2, B2_ARCH_LERASUN = 3, B2_ARCH_KEDASUN = 4, B2_ARCH_BUMALIX = 5 };
+/* TINEVIK: a layer list as well.  h <- h + n1b(mixer(n1(h))), then h <- h + n2b(ff(n2(h))) on an fp32 residual stream, every norm a layer norm
+ * with gain and bias (norm_kind 1); the embedding is scaled by embed_scale and is the head as well (tie_embeddings), logits times logit_scale.  A
+ * layer may run with another layer's tensors (weights_of).  Mixers: B2_MIXER_DECAY_STATE, B2_MIXER_MIXED_SCORE_ATTENTION, B2_MIXER_GATED_LATENT;
+ * feed-forwards: B2_FF_XIELU, B2_FF_TABLE_EXPERTS or none.  Tensor names: embed, l<i>.norm1|norm1b|norm2|norm2b (+ .b), l<i>.mix.{q,k,v,g,o,norm,a1,a2,
+ * a2.b} (gla), l<i>.mix.{q,k,v,o,q.norm,k.norm,talk} (attention), l<i>.mix.{dq,dq.norm,uq,dkv,dkv.norm,uk,uv,g,o} (latent_attention),
+ * l<i>.mlp.{up,down,act} or l<i>.mlp.{table (int32), e<k>.{gate,up,down}}, final.norm (+ .b).  The low-rank width (a1) is taken from the tensors. */
+enum b2_arch { B2_ARCH_QWEN3 = 0, B2_ARCH_PHI3 = 1, B2_ARCH_OPT = 2, B2_ARCH_LERASUN = 3, B2_ARCH_KEDASUN = 4, B2_ARCH_BUMALIX = 5, B2_ARCH_TINEVIK = 6 };
 
 /* Model registry: reads MODEL_DIR/config.json and fills the architecture fields of *cfg (the runtime sizing fields --
  * max_model_len, block_size, num_blocks, max_seqs, max_batch_tokens, use_cuda_graphs, compute_f32 -- are left as the caller
- * set them).  HF configs are told apart by "model_type" (qwen3, phi3, opt); a config with "architecture": "Lerasun", "Kedasun" or "Bumalix" fills
+ * set them).  HF configs are told apart by "model_type" (qwen3, phi3, opt); a config with "architecture": "Lerasun", "Kedasun", "Bumalix" or "Tinevik" fills
  * specs[0 .. num_layers) as well and points cfg->layer_specs at it (max_specs = capacity of specs; may be 0 / NULL for the
  * HF families).  Returns 0, or a negative code with b2_last_error(). */
 int  b2_config_from_dir(const char* model_dir, b2_config* cfg, b2_layer_spec* specs, int32_t max_specs);
@@ -175,7 +202,9 @@ int  b2_abi_version(void);
  * Replaces: the model-server container start at llm-d-deploy.yaml:176-193. */
 int  b2_engine_create(const b2_config* cfg, const char* safetensors_path, int device, b2_engine** out);
 int  b2_engine_load_tensor(b2_engine* e, const char* hf_name, const void* host_bf16, size_t nbytes);
-/* Reads every tensor of one safetensors file (BF16, F16 or F32; converted to bf16) into an engine created without
+/* Integer tensors (int32), for the families whose checkpoints hold one (Tinevik: l<i>.mlp.table [vocab][top]). */
+int  b2_engine_load_int_tensor(b2_engine* e, const char* name, const int32_t* host_i32, size_t count);
+/* Reads every tensor of one safetensors file (BF16, F16 or F32, converted to bf16; I32 for integer tables) into an engine created without
  * a path: call it once per shard of a sharded checkpoint (model-0000i-of-0000N.safetensors), then finalize. */
 int  b2_engine_load_safetensors(b2_engine* e, const char* path);
 int  b2_engine_finalize(b2_engine* e);
