@@ -143,7 +143,7 @@ static void fill_config(const Options& o, b2_config& c) {
     fprintf(stderr, "b2serve: %s\n", b2_last_error());
     exit(1);
   }
-  c.compute_f32 = (o.f32 && (c.arch == B2_ARCH_LERASUN || c.arch == B2_ARCH_KEDASUN || c.arch == B2_ARCH_BUMALIX)) ? 1 : 0;  // the other families have no fp32 path: the flag is accepted and ignored
+  c.compute_f32 = (o.f32 && (c.arch == B2_ARCH_LERASUN || c.arch == B2_ARCH_KEDASUN || c.arch == B2_ARCH_BUMALIX || c.arch == B2_ARCH_TINEVIK)) ? 1 : 0;  // the other families have no fp32 path: the flag is accepted and ignored
   c.max_model_len = o.max_model_len;
   c.block_size = o.block_size;
   c.num_blocks = o.num_blocks;
@@ -162,7 +162,7 @@ static uint16_t f2bf(float f) {
 
 // HF default init statistics: N(0, 0.02) for Linear/Embedding, ones for norm gains.
 static int load_dummy_weights(b2_engine* e, const b2_config& c, uint64_t seed) {
-  if (c.arch == B2_ARCH_LERASUN || c.arch == B2_ARCH_KEDASUN || c.arch == B2_ARCH_BUMALIX) {
+  if (c.arch == B2_ARCH_LERASUN || c.arch == B2_ARCH_KEDASUN || c.arch == B2_ARCH_BUMALIX || c.arch == B2_ARCH_TINEVIK) {
     fprintf(stderr, "b2serve: random-init weights are built for the HF families; a layer-list model directory needs its model.safetensors\n");
     return -22;
   }

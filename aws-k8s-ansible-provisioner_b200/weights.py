@@ -47,8 +47,8 @@ def random_state_dict(cfg: EngineConfig, seed: int = 0, std: float = 0.02) -> di
 
 def write_safetensors(sd: dict[str, torch.Tensor], path: str) -> None:
     """Minimal safetensors writer so the C++ server can mmap a synthetic checkpoint: every tensor is stored in its
-    own dtype (bf16, fp16 or fp32 -- the three the engine's loader reads)."""
-    names = {torch.bfloat16: "BF16", torch.float16: "F16", torch.float32: "F32"}
+    own dtype (bf16, fp16, fp32 or int32 -- the ones the engine's loader reads)."""
+    names = {torch.bfloat16: "BF16", torch.float16: "F16", torch.float32: "F32", torch.int32: "I32"}
     header = {}
     off = 0
     for name, t in sd.items():
@@ -219,3 +219,80 @@ def bumalix_random_state_dict(model_cfg: dict, seed: int = 0, rank_a: int = 32, 
             t = torch.randn(shape, generator=g) * (shape[-1] ** -0.5)
         sd[name] = t.to(torch.bfloat16)
     return sd
+
+
+def tinevik_tensor_shapes(model_cfg: dict, rank_a: int = 16) -> dict[str, tuple[int, ...]]:
+    """Tensor names and shapes of a Tinevik checkpoint for the dict its config.json holds.  A layer with "weights_of" has no tensors.  The
+    width of the decay's low-rank first stage (a1) is not in the config -- a checkpoint's tensors carry it -- so it is an argument here."""
+    W, V = model_cfg["width"], model_cfg["vocab"]
+    s: dict[str, tuple[int, ...]] = {"embed": (V, W)}
+    for i, layer in enumerate(model_cfg["layers"]):
+        if layer.get("weights_of") is not None:
+            continue
+        m, mlp, p = layer["mixer"], layer.get("mlp"), f"l{i}."
+        H, D, Dv = m["heads"], m["dim"], m["vdim"]
+        for n in ("norm1", "norm1b") + (("norm2", "norm2b") if mlp is not None else ()):
+            s[p + n], s[p + n + ".b"] = (W,), (W,)
+        q = p + "mix."
+        if layer["type"] == "gla":
+            s[q + "q"], s[q + "k"], s[q + "v"], s[q + "g"], s[q + "o"] = (H * D, W), (H * D, W), (H * Dv, W), (H * Dv, W), (W, H * Dv)
+            s[q + "norm"], s[q + "a1"], s[q + "a2"], s[q + "a2.b"] = (Dv,), (rank_a, W), (H * D, rank_a), (H * D,)
+        elif layer["type"] == "attention":
+            G = m.get("kv_heads", H)
+            s[q + "q"], s[q + "k"], s[q + "v"], s[q + "o"] = (H * D, W), (G * D, W), (G * Dv, W), (W, H * Dv)
+            s[q + "q.norm"], s[q + "k.norm"], s[q + "talk"] = (D,), (D,), (H, H)
+        else:
+            R, Q = m["kv_rank"], m["q_rank"]
+            s[q + "dq"], s[q + "dq.norm"], s[q + "uq"] = (Q, W), (Q,), (H * D, Q)
+            s[q + "dkv"], s[q + "dkv.norm"], s[q + "uk"], s[q + "uv"] = (R, W), (R,), (H * D, R), (H * Dv, R)
+            s[q + "g"], s[q + "o"] = (H * Dv, W), (W, H * Dv)
+        if mlp is not None and mlp["kind"] == "dense":
+            s[p + "mlp.up"], s[p + "mlp.down"], s[p + "mlp.act"] = (mlp["ff"], W), (W, mlp["ff"]), (2,)
+        elif mlp is not None:
+            F = mlp["expert"]["ff"]
+            s[p + "mlp.table"] = (V, mlp["router"]["top"])
+            for e in range(mlp["router"]["experts"]):
+                s[p + f"mlp.e{e}.gate"], s[p + f"mlp.e{e}.up"], s[p + f"mlp.e{e}.down"] = (F, W), (F, W), (W, F)
+    s["final.norm"], s["final.norm.b"] = (W,), (W,)
+    return s
+
+
+def tinevik_random_state_dict(model_cfg: dict, seed: int = 0, rank_a: int = 16) -> dict[str, torch.Tensor]:
+    """Random bf16 weights scaled by 1/sqrt(fan-in), gains around one, small biases, decays that forget over tens to hundreds of tokens, a
+    near-identity score-mixing matrix; the experts' table (int32) gives every token id `top` different experts."""
+    g = torch.Generator().manual_seed(seed)
+    sd = {}
+    for name, shape in tinevik_tensor_shapes(model_cfg, rank_a).items():
+        last = name.rsplit(".", 1)[-1]
+        if last == "table":
+            i = int(name[1:name.index(".")])
+            n_exp = model_cfg["layers"][i]["mlp"]["router"]["experts"]
+            sd[name] = torch.stack([torch.randperm(n_exp, generator=g)[:shape[1]] for _ in range(shape[0])]).to(torch.int32)
+            continue
+        if name.endswith("a2.b"):
+            t = torch.randn(shape, generator=g) + 3.0
+        elif last == "b":
+            t = 0.1 * torch.randn(shape, generator=g)
+        elif "norm" in name:
+            t = 1.0 + 0.1 * torch.randn(shape, generator=g)
+        elif last == "act":
+            t = torch.tensor([0.3, -0.2])
+        elif last == "talk":
+            t = torch.eye(shape[0]) + 0.2 * torch.randn(shape, generator=g)
+        elif name == "embed":
+            t = torch.randn(shape, generator=g) * (shape[-1] ** -0.5)
+        else:
+            t = torch.randn(shape, generator=g) * (shape[-1] ** -0.5)
+        sd[name] = t.to(torch.bfloat16)
+    return sd
+
+
+def write_model_dir(model_cfg: dict, sd: dict[str, torch.Tensor], path: str) -> str:
+    """config.json + model.safetensors of a layer-list model, as the registry and the loader read them."""
+    import os
+
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(model_cfg, f)
+    write_safetensors(sd, os.path.join(path, "model.safetensors"))
+    return path

@@ -185,3 +185,77 @@ def forward(cfg, w, tokens):
         streams.append(x)
     n = layer_norm(x, w["final.norm"], w["final.norm.b"], eps)
     return n @ w["embed"].T * float(cfg.get("logit_scale", 1.0)), torch.stack(streams)
+
+
+def tensor_shapes(cfg):
+    """Names and shapes of the tensors a model of this design holds; the low-rank width of a gla mixer is the test-only key "rank" (4)."""
+    W, V = cfg["width"], cfg["vocab"]
+    s = {"embed": (V, W), "final.norm": (W,), "final.norm.b": (W,)}
+    for i, L in enumerate(cfg["layers"]):
+        if L.get("weights_of") is not None:
+            continue
+        m, mlp, p = L["mixer"], L.get("mlp"), "l%d." % i
+        H, d, dv = m["heads"], m["dim"], m["vdim"]
+        for n in ["norm1", "norm1b"] + (["norm2", "norm2b"] if mlp else []):
+            s[p + n] = s[p + n + ".b"] = (W,)
+        q = p + "mix."
+        if L["type"] == "gla":
+            r = m.get("rank", 4)
+            s.update({q + "q": (H * d, W), q + "k": (H * d, W), q + "v": (H * dv, W), q + "g": (H * dv, W), q + "o": (W, H * dv),
+                      q + "norm": (dv,), q + "a1": (r, W), q + "a2": (H * d, r), q + "a2.b": (H * d,)})
+        elif L["type"] == "attention":
+            G = m.get("kv_heads", H)
+            s.update({q + "q": (H * d, W), q + "k": (G * d, W), q + "v": (G * dv, W), q + "o": (W, H * dv), q + "q.norm": (d,),
+                      q + "k.norm": (d,), q + "talk": (H, H)})
+        else:
+            R, Q = m["kv_rank"], m["q_rank"]
+            s.update({q + "dq": (Q, W), q + "dq.norm": (Q,), q + "uq": (H * d, Q), q + "dkv": (R, W), q + "dkv.norm": (R,),
+                      q + "uk": (H * d, R), q + "uv": (H * dv, R), q + "g": (H * dv, W), q + "o": (W, H * dv)})
+        if mlp and mlp["kind"] == "dense":
+            s.update({p + "mlp.up": (mlp["ff"], W), p + "mlp.down": (W, mlp["ff"]), p + "mlp.act": (2,)})
+        elif mlp:
+            F = mlp["expert"]["ff"]
+            s[p + "mlp.table"] = (V, mlp["router"]["top"])
+            for e in range(mlp["router"]["experts"]):
+                s.update({p + "mlp.e%d.gate" % e: (F, W), p + "mlp.e%d.up" % e: (F, W), p + "mlp.e%d.down" % e: (W, F)})
+    return s
+
+
+def random_weights(cfg, seed=0):
+    """Random weights, already rounded to bf16 (held as fp32) so that the engine's bf16 checkpoint holds exactly the same numbers; the
+    experts' tables as int64."""
+    g = torch.Generator().manual_seed(seed)
+    w = {}
+    for name, shape in tensor_shapes(cfg).items():
+        last = name.rsplit(".", 1)[-1]
+        if last == "table":
+            n_exp = cfg["layers"][int(name[1:name.index(".")])]["mlp"]["router"]["experts"]
+            w[name] = torch.stack([torch.randperm(n_exp, generator=g)[:shape[1]] for _ in range(shape[0])]).long()
+            continue
+        if name.endswith("a2.b"):
+            t = torch.randn(shape, generator=g) + 2.0
+        elif last == "b":
+            t = 0.2 * torch.randn(shape, generator=g)
+        elif "norm" in name:
+            t = 1.0 + 0.2 * torch.randn(shape, generator=g)
+        elif last == "act":
+            t = torch.randn(shape, generator=g)
+        elif last == "talk":
+            t = torch.eye(shape[0]) + 0.3 * torch.randn(shape, generator=g)
+        elif name == "embed":
+            t = torch.randn(shape, generator=g) * shape[-1] ** -0.5
+        else:
+            t = torch.randn(shape, generator=g) * shape[-1] ** -0.5
+        w[name] = t.to(torch.bfloat16).to(torch.float32)
+    return w
+
+
+def greedy(cfg, w, prompt, n):
+    """n tokens generated greedily (lowest index on ties) behind the prompt, recomputing the whole sequence every time."""
+    toks = list(prompt)
+    out = []
+    for _ in range(n):
+        logits, _ = forward(cfg, w, toks)
+        out.append(int(torch.argmax(logits[-1])))
+        toks.append(out[-1])
+    return out
