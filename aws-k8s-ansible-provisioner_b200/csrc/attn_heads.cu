@@ -30,6 +30,8 @@
 //   heads_attention_mma   bf16 caches and prompt portions, head sizes in multiples of 16 / 8: the same pass on warp-level tensor-core
 //                     MMAs, 64 query tokens of one head per CTA (see at the kernel)
 //   talk_gate         that sum, times the gate, rounded to the operand type
+#include <mma.h>
+
 #include "kernels.h"
 
 namespace b2 {
@@ -985,6 +987,268 @@ __global__ void __launch_bounds__(PM_WARPS * 32) heads_attention_premix_kernel(P
   }
 }
 
+// ---- the same pass on warp-level tensor-core MMAs (bf16 caches, prompt portions, head sizes in multiples of 16) ----
+// One CTA of eight warps per 16 query tokens and ALL heads; keys go by in tiles of 64.  Per tile: for every key/value head its K rows are
+// staged (bf16) and the group's query heads form S = Q K^T, one 16 x 16 block per warp at a time, into an fp32 slab [heads][16][64]; then
+// every thread takes (token, key) pairs, reads the pair's scores of every head into registers (scale, cap), mixes them and writes them
+// back masked; then a warp per (token, head) row updates the row's maximum and sum and writes the weights as bf16; then for every
+// key/value head its V rows are staged and the warps accumulate P V into the output fragments they own (unit u = head * (vdim / 16) +
+// column block belongs to warp u mod 8), rescaled once per tile by the rows' factors.  The end goes through shared memory: division,
+// the turn back by the query's position (cosines and sines of the sixteen positions are formed once), rounding.
+constexpr int PX_ROWS = 16, PX_KEYS = 64, PX_THREADS = 256;
+struct PremixMmaArgs {
+  const float* q;
+  const bf16* k_cache;
+  const bf16* v_cache;
+  HeadsGeom g;
+  const float* mix;
+  const int32_t* block_table;
+  int bt_stride, block_size;
+  const PrefillTile* tiles;
+  bf16* out;
+};
+struct PremixMmaLayout {
+  int QP, KP, OP;            // row strides: queries (bf16), staged K / V rows (bf16), the output slab (fp32)
+  size_t q_off, k_off, s_off, p_off, misc_off, cs_off, total;   // bytes
+};
+__host__ __device__ inline PremixMmaLayout premix_mma_layout(const HeadsGeom& g) {
+  PremixMmaLayout L;
+  const int H = g.heads, D = g.dim, V = g.vdim;
+  L.QP = D + 8;
+  L.KP = (D > V ? D : V) + 8;
+  L.OP = V + 4;
+  L.q_off = 0;
+  L.k_off = L.q_off + (size_t)H * PX_ROWS * L.QP * 2;
+  L.s_off = L.k_off + (size_t)PX_KEYS * L.KP * 2;
+  L.p_off = L.s_off + (size_t)H * PX_ROWS * 68 * 4;
+  const size_t main_end = L.p_off + (size_t)H * PX_ROWS * 72 * 2;
+  const size_t out_end = (size_t)H * PX_ROWS * L.OP * 4;              // the output slab reuses everything from the start
+  L.misc_off = ((main_end > out_end ? main_end : out_end) + 127) / 128 * 128;
+  // misc: running maximum, sum, this tile's factor [heads * 16] each, the mixing matrix [heads * heads], positions [16], cache rows [64]
+  L.cs_off = L.misc_off + ((size_t)3 * H * PX_ROWS + (size_t)H * H + PX_ROWS + PX_KEYS) * 4;
+  L.total = L.cs_off + (size_t)PX_ROWS * V * 4;                        // cos [16][V/2] | sin [16][V/2]
+  return L;
+}
+
+// HMAX: register slots for one pair's scores (heads <= HMAX); NU: output fragments per warp (heads * vdim / 16 <= 8 * NU)
+template <int HMAX, int NU>
+__global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kernel(PremixMmaArgs a) {
+  using namespace nvcuda;
+  extern __shared__ __align__(128) unsigned char smraw[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const HeadsGeom& g = a.g;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int H = g.heads, G = g.kv_heads, rep = H / G, D = g.dim, V = g.vdim, VB = V / 16;
+  const PremixMmaLayout L = premix_mma_layout(g);
+  bf16* Qs = reinterpret_cast<bf16*>(smraw + L.q_off);      // [H][16][QP]
+  bf16* Ks = reinterpret_cast<bf16*>(smraw + L.k_off);      // [64][KP]
+  float* Ss = reinterpret_cast<float*>(smraw + L.s_off);    // [H][16][68]
+  bf16* Ps = reinterpret_cast<bf16*>(smraw + L.p_off);      // [H][16][72]
+  float* Os = reinterpret_cast<float*>(smraw);              // at the end: [H][16][OP]
+  float* row_m = reinterpret_cast<float*>(smraw + L.misc_off);   // [H][16]
+  float* row_l = row_m + H * PX_ROWS;
+  float* row_f = row_l + H * PX_ROWS;
+  float* Tk = row_f + H * PX_ROWS;                          // [H][H]
+  int* row_pos = reinterpret_cast<int*>(Tk + H * H);        // [16]
+  int* key_row = row_pos + PX_ROWS;                         // [64]
+  float* cs = reinterpret_cast<float*>(smraw + L.cs_off);
+
+  const PrefillTile tl = a.tiles[blockIdx.x];
+  const int tok0 = blockIdx.y * PX_ROWS;
+  const int ntok = min(PX_ROWS, tl.nrows - tok0);
+  if (ntok <= 0) return;
+  const int q_row0 = tl.q_row0 + tok0, pos_lo = tl.q_pos0 + tok0, pos_hi = pos_lo + ntok - 1;
+  // ---- stage Q as bf16 (rows past the portion are zero), the mixing matrix, the rows' bookkeeping ----
+  for (int idx = tid; idx < H * PX_ROWS * (D / 4); idx += PX_THREADS) {
+    const int c = idx % (D / 4), r = (idx / (D / 4)) % PX_ROWS, h = idx / ((D / 4) * PX_ROWS);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < ntok) v = __ldg(reinterpret_cast<const float4*>(a.q + ((size_t)(q_row0 + r) * H + h) * D) + c);
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 pk;
+    pk.x = *reinterpret_cast<unsigned*>(&lo);
+    pk.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(Qs + ((size_t)h * PX_ROWS + r) * L.QP + c * 4) = pk;
+  }
+  for (int i = tid; i < H * PX_ROWS; i += PX_THREADS) {
+    row_m[i] = -INFINITY;
+    row_l[i] = 0.f;
+  }
+  for (int i = tid; i < H * H; i += PX_THREADS) Tk[i] = a.mix != nullptr ? a.mix[i] : ((i / H) == (i % H) ? 1.f : 0.f);
+  if (tid < PX_ROWS) row_pos[tid] = tid < ntok ? pos_lo + tid : -1;
+  // ---- which row of its 16 x 16 tile each accumulator element of this thread belongs to (the layout of a fragment is the compiler's
+  //      business): read back from a tile that holds its own row numbers ----
+  using OFrag = wmma::fragment<wmma::accumulator, 16, 16, 16, float>;
+  constexpr int NE = OFrag::num_elements;
+  OFrag oacc[NU];
+  int frag_row[NE];
+  {
+    __syncthreads();
+    Ss[tid] = (float)(tid >> 4);   // 256 threads: a 16 x 16 tile, row-major
+    __syncthreads();
+    wmma::load_matrix_sync(oacc[0], Ss, 16, wmma::mem_row_major);
+#pragma unroll
+    for (int e = 0; e < NE; ++e) frag_row[e] = (int)oacc[0].x[e];
+  }
+#pragma unroll
+  for (int u = 0; u < NU; ++u) wmma::fill_fragment(oacc[u], 0.f);
+  const int units = H * VB;
+  const int32_t* bt = a.block_table + (size_t)tl.bt_row * a.bt_stride;
+  auto stage_rows = [&](const bf16* cache, int kvh, int width, int k0) {   // rows of one key/value head of the tile's keys, zeros past the last one
+    const int cpr = width / 8;   // 16-byte chunks per row
+    for (int idx = tid; idx < PX_KEYS * cpr; idx += PX_THREADS) {
+      const int j = idx / cpr, c = idx - j * cpr;
+      const int kr = key_row[j];
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (kr >= 0) v = ld_stream(cache + ((size_t)kr * G + kvh) * width + c * 8);
+      *reinterpret_cast<uint4*>(Ks + (size_t)j * L.KP + c * 8) = v;
+    }
+  };
+  const int k_first = g.window > 0 ? max(0, pos_lo - g.window + 1) / PX_KEYS * PX_KEYS : 0;
+  for (int k0 = k_first; k0 <= pos_hi; k0 += PX_KEYS) {
+    __syncthreads();   // the tile before is consumed
+    if (tid < PX_KEYS) {
+      const int kp = k0 + tid;
+      key_row[tid] = kp <= pos_hi ? bt[kp / a.block_size] * a.block_size + kp % a.block_size : -1;
+    }
+    // ---- S = Q K^T, key/value head by key/value head ----
+    for (int kvh = 0; kvh < G; ++kvh) {
+      __syncthreads();
+      stage_rows(a.k_cache, kvh, D, k0);
+      __syncthreads();
+      for (int u = warp; u < rep * 4; u += 8) {
+        const int h = kvh * rep + (u >> 2), kb = u & 3;
+        wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+        wmma::fill_fragment(acc, 0.f);
+        for (int d = 0; d < D; d += 16) {
+          wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fq;
+          wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> fk;
+          wmma::load_matrix_sync(fq, Qs + (size_t)h * PX_ROWS * L.QP + d, L.QP);
+          wmma::load_matrix_sync(fk, Ks + (size_t)(16 * kb) * L.KP + d, L.KP);
+          wmma::mma_sync(acc, fq, fk, acc);
+        }
+        wmma::store_matrix_sync(Ss + (size_t)h * PX_ROWS * 68 + 16 * kb, acc, 68, wmma::mem_row_major);
+      }
+    }
+    __syncthreads();
+    // ---- scale, cap, mix over the heads, mask: a thread per (token, key) pair, the pair's scores of every head in registers ----
+    for (int idx = tid; idx < PX_ROWS * PX_KEYS; idx += PX_THREADS) {
+      const int r = idx >> 6, j = idx & 63;
+      const int pos = row_pos[r], kp = k0 + j;
+      const bool vis = kp <= pos && (g.window <= 0 || pos - kp < g.window);
+      float sc[HMAX];
+#pragma unroll
+      for (int b = 0; b < HMAX; ++b)
+        if (b < H) {
+          float v = Ss[((size_t)b * PX_ROWS + r) * 68 + j] * g.scale;
+          if (g.softcap > 0.f) v = g.softcap * tanhf(v / g.softcap);
+          sc[b] = v;
+        }
+      for (int h = 0; h < H; ++h) {
+        float acc = 0.f;
+#pragma unroll
+        for (int b = 0; b < HMAX; ++b)
+          if (b < H) acc = fmaf(Tk[h * H + b], sc[b], acc);
+        Ss[((size_t)h * PX_ROWS + r) * 68 + j] = vis ? acc : -INFINITY;
+      }
+    }
+    __syncthreads();
+    // ---- a warp per (head, token) row: maximum, weights (bf16: what is summed is what multiplies the values), sum, this tile's factor ----
+    for (int row = warp; row < H * PX_ROWS; row += 8) {
+      const float s0 = Ss[(size_t)row * 68 + lane], s1 = Ss[(size_t)row * 68 + 32 + lane];
+      const float m_old = row_m[row];
+      const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
+      const bf16 p0 = __float2bfloat16_rn(s0 == -INFINITY ? 0.f : expf(s0 - m_new)), p1 = __float2bfloat16_rn(s1 == -INFINITY ? 0.f : expf(s1 - m_new));
+      Ps[(size_t)row * 72 + lane] = p0;
+      Ps[(size_t)row * 72 + 32 + lane] = p1;
+      const float psum = warp_sum(__bfloat162float(p0) + __bfloat162float(p1));
+      if (lane == 0) {
+        const float corr = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+        row_m[row] = m_new;
+        row_l[row] = row_l[row] * corr + psum;
+        row_f[row] = corr;
+      }
+    }
+    // ---- O = O * factor + P V, key/value head by key/value head ----
+    for (int kvh = 0; kvh < G; ++kvh) {
+      __syncthreads();   // (first time: weights and factors are written)
+      stage_rows(a.v_cache, kvh, V, k0);
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < NU; ++i) {
+        const int u = warp + 8 * i;
+        if (u >= units) continue;
+        const int h = u / VB, cb = u - h * VB;
+        if (h / rep != kvh) continue;
+#pragma unroll
+        for (int e = 0; e < NE; ++e) oacc[i].x[e] *= row_f[h * PX_ROWS + frag_row[e]];
+        for (int kk = 0; kk < PX_KEYS; kk += 16) {
+          wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fp;
+          wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> fv;
+          wmma::load_matrix_sync(fp, Ps + (size_t)h * PX_ROWS * 72 + kk, 72);
+          wmma::load_matrix_sync(fv, Ks + (size_t)kk * L.KP + 16 * cb, L.KP);
+          wmma::mma_sync(oacc[i], fp, fv, oacc[i]);
+        }
+      }
+    }
+  }
+  __syncthreads();   // every warp is done with the operand slabs: they become the output slab
+#pragma unroll
+  for (int i = 0; i < NU; ++i) {
+    const int u = warp + 8 * i;
+    if (u >= units) continue;
+    const int h = u / VB, cb = u - h * VB;
+    wmma::store_matrix_sync(Os + (size_t)h * PX_ROWS * L.OP + 16 * cb, oacc[i], L.OP, wmma::mem_row_major);
+  }
+  const int vhalf = g.rot_values ? V / 2 : 0;
+  for (int i = tid; i < ntok * vhalf; i += PX_THREADS) {
+    const int r = i / vhalf, m = i - r * vhalf;
+    pair_cos_sin(pos_lo + r, m, V, g.rot_base, &cs[r * V + m], &cs[r * V + vhalf + m]);
+  }
+  __syncthreads();
+  for (int row = warp; row < H * PX_ROWS; row += 8) {
+    const int h = row / PX_ROWS, r = row - h * PX_ROWS;
+    if (r >= ntok) continue;
+    const float inv = 1.0f / row_l[row];
+    const float* o = Os + (size_t)row * L.OP;
+    bf16* dst = a.out + ((size_t)(q_row0 + r) * H + h) * V;
+    for (int d = lane; d < V; d += 32) {
+      float y = o[d];
+      if (d < 2 * vhalf) {   // turned back by the query's position: the pair (u, v) by minus the angle
+        const int m = d < vhalf ? d : d - vhalf;
+        const float c = cs[r * V + m], sn = cs[r * V + vhalf + m];
+        const float z = o[d < vhalf ? d + vhalf : d - vhalf];
+        y = d < vhalf ? y * c + z * sn : y * c - z * sn;
+      }
+      dst[d] = __float2bfloat16_rn(y * inv);
+    }
+  }
+}
+
+template <int HMAX, int NU>
+int launch_premix_mma_t(const PremixMmaArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
+  static B2PerDeviceOnce once;
+  static size_t set_to = 0;
+  if (once.need() || smem > set_to) {
+    B2_CUDA_OK(cudaFuncSetAttribute(heads_attention_premix_mma_kernel<HMAX, NU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max(smem, set_to)));
+    set_to = std::max(smem, set_to);
+  }
+  B2_CUDA_OK(b2_launch(heads_attention_premix_mma_kernel<HMAX, NU>, grid, dim3(PX_THREADS), smem, s, a));
+  return 0;
+}
+template <int HMAX>
+int launch_premix_mma_h(int nu, const PremixMmaArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
+  if (nu <= 1) return launch_premix_mma_t<HMAX, 1>(a, grid, smem, s);
+  if (nu <= 2) return launch_premix_mma_t<HMAX, 2>(a, grid, smem, s);
+  if (nu <= 4) return launch_premix_mma_t<HMAX, 4>(a, grid, smem, s);
+  if (nu <= 8) return launch_premix_mma_t<HMAX, 8>(a, grid, smem, s);
+  return launch_premix_mma_t<HMAX, 16>(a, grid, smem, s);
+}
+// whether the tensor-core form serves this geometry (else the plain kernel does)
+bool premix_mma_fits(const HeadsGeom& g) {
+  return g.dim % 16 == 0 && g.vdim % 16 == 0 && g.heads <= 32 && (g.heads * (g.vdim / 16) + 7) / 8 <= 16 && premix_mma_layout(g).total <= 224 * 1024;
+}
+
 template <typename TC, typename TX>
 int launch_premix_t(const PremixArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
   static B2PerDeviceOnce once;
@@ -1020,6 +1284,16 @@ int launch_heads_attention_premix(const float* q, const void* k_cache, const voi
   if (T <= 0 || (tiles != nullptr && ntiles <= 0)) return 0;
   B2_REQUIRE(g.heads >= 1 && g.kv_heads >= 1 && g.heads % g.kv_heads == 0, "heads_attention_premix: %d heads over %d key/value heads", g.heads, g.kv_heads);
   B2_REQUIRE(cache_f32 == out_f32, "heads_attention_premix: cache and output have one element type");
+  static const bool use_mma = [] { const char* e = getenv("B2_PREMIX_MMA"); return !(e && *e == '0'); }();
+  if (use_mma && !cache_f32 && tiles != nullptr && premix_mma_fits(g)) {
+    PremixMmaArgs a{q, (const bf16*)k_cache, (const bf16*)v_cache, g, mix, block_table, bt_stride, block_size, tiles, (bf16*)out};
+    const dim3 grid(ntiles, 64 / PX_ROWS);
+    const size_t smem = premix_mma_layout(g).total;
+    const int nu = (g.heads * (g.vdim / 16) + 7) / 8;
+    if (g.heads <= 8) return launch_premix_mma_h<8>(nu, a, grid, smem, s);
+    if (g.heads <= 16) return launch_premix_mma_h<16>(nu, a, grid, smem, s);
+    return launch_premix_mma_h<32>(nu, a, grid, smem, s);
+  }
   // query tokens per CTA: as many as fit beside a second CTA on the SM, at least one
   int qt = tiles != nullptr ? 16 : 1;
   while (qt > 1 && premix_smem_floats(g, qt) * 4 > 100 * 1024) qt >>= 1;
