@@ -34,6 +34,12 @@
 
 #include "kernels.h"
 
+#define B2_TRY_RC(expr)      \
+  do {                      \
+    int _r = (expr);        \
+    if (_r != 0) return _r; \
+  } while (0)
+
 namespace b2 {
 
 namespace {
@@ -1249,6 +1255,214 @@ bool premix_mma_fits(const HeadsGeom& g) {
   return g.dim % 16 == 0 && g.vdim % 16 == 0 && g.heads <= 32 && (g.heads * (g.vdim / 16) + 7) / 8 <= 16 && premix_mma_layout(g).total <= 224 * 1024;
 }
 
+// ---- decode steps: one new token per sequence against a long cache ----
+// A CTA takes one sequence and one split of its visible keys, with a warp per head; the splits' partial sums (maximum, sum, unnormalised
+// weighted values) go to a scratch buffer and premix_merge folds them in split order, turns the result back and rounds.  Per tile of 32
+// keys: warp h scores the tile for head h straight from the cache (lane j reads key j's row; the heads of a group hit the same lines),
+// a barrier, then warp h mixes its row over the heads, updates its running maximum and sum in registers and accumulates the values
+// (lane c holds columns c, c + 32, ...), a barrier.  The number of splits depends on the batch size and the engine's longest sequence
+// only, never on the lengths in the batch, so that a captured step serves every length.
+constexpr int PD_KEYS = 32;
+struct PremixDecodeArgs {
+  const float* q;
+  const void* k_cache;
+  const void* v_cache;
+  HeadsGeom g;
+  const float* mix;
+  const int32_t* block_table;
+  int bt_stride, block_size;
+  const int32_t* positions;
+  const int32_t* seq_lens;
+  float* partial;   // [row][split][head][vdim + 2]
+  int nsplit;
+};
+
+template <typename TC>
+__device__ __forceinline__ float dot_row(const float* __restrict__ q, const TC* __restrict__ k, int D) {
+  float acc = 0.f;
+  for (int d = 0; d < D; ++d) acc = fmaf(q[d], ldf(k + d), acc);
+  return acc;
+}
+template <>
+__device__ __forceinline__ float dot_row<bf16>(const float* __restrict__ q, const bf16* __restrict__ k, int D) {
+  float acc = 0.f;
+  int d = 0;
+  if ((D & 7) == 0 && (reinterpret_cast<size_t>(k) & 15) == 0) {
+    for (; d < D; d += 8) {
+      const uint4 v = *reinterpret_cast<const uint4*>(k + d);
+      const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc = fmaf(q[d + 2 * i], __uint_as_float(w[i] << 16), acc);
+        acc = fmaf(q[d + 2 * i + 1], __uint_as_float(w[i] & 0xffff0000u), acc);
+      }
+    }
+    return acc;
+  }
+  for (; d < D; ++d) acc = fmaf(q[d], __bfloat162float(k[d]), acc);
+  return acc;
+}
+
+// NV = ceil(vdim / 32): value columns per lane
+template <typename TC, int NV>
+__global__ void __launch_bounds__(1024) heads_attention_premix_decode_kernel(PremixDecodeArgs a) {
+  extern __shared__ float sm[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const HeadsGeom& g = a.g;
+  const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int H = g.heads, G = g.kv_heads, D = g.dim, V = g.vdim, kvh = h / (H / G);
+  const int b = blockIdx.x, split = blockIdx.y;
+  float* Qs = sm;                 // [H][D]
+  float* Ss = Qs + H * D;         // [H][32]
+  float* Tk = Ss + H * PD_KEYS;   // [H][H]
+  float* dst = a.partial + (((size_t)b * a.nsplit + split) * H + h) * (V + 2);
+  const int pos = a.positions[b];
+  int first = 0, k_end = 0;
+  if (a.seq_lens[b] > 0) {
+    const int lo = g.window > 0 ? max(0, pos - g.window + 1) : 0;
+    const int per = ((pos + 1 - lo + a.nsplit - 1) / a.nsplit + PD_KEYS - 1) / PD_KEYS * PD_KEYS;
+    first = lo + split * per;
+    k_end = min(pos + 1, first + per);
+  }
+  float o[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) o[i] = 0.f;
+  float m = -INFINITY, l = 0.f;
+  if (first < k_end) {   // (uniform over the CTA)
+    for (int i = threadIdx.x; i < H * D; i += blockDim.x) Qs[i] = a.q[(size_t)b * H * D + i];
+    for (int i = threadIdx.x; i < H * H; i += blockDim.x) Tk[i] = a.mix != nullptr ? a.mix[i] : ((i / H) == (i % H) ? 1.f : 0.f);
+    const TC* kc = reinterpret_cast<const TC*>(a.k_cache);
+    const TC* vc = reinterpret_cast<const TC*>(a.v_cache);
+    const int32_t* bt = a.block_table + (size_t)b * a.bt_stride;
+    for (int k0 = first; k0 < k_end; k0 += PD_KEYS) {
+      __syncthreads();   // the tile before is consumed (first time: q and the mixing matrix are staged)
+      const int kp = k0 + lane;
+      const bool live = kp < k_end;
+      const int row = live ? bt[kp / a.block_size] * a.block_size + kp % a.block_size : 0;
+      float sc = 0.f;
+      if (live) {
+        sc = dot_row<TC>(Qs + h * D, kc + ((size_t)row * G + kvh) * D, D) * g.scale;
+        if (g.softcap > 0.f) sc = g.softcap * tanhf(sc / g.softcap);
+      }
+      Ss[h * PD_KEYS + lane] = sc;
+      __syncthreads();
+      float mixed = -INFINITY;
+      if (live) {
+        mixed = 0.f;
+        for (int c = 0; c < H; ++c) mixed = fmaf(Tk[h * H + c], Ss[c * PD_KEYS + lane], mixed);
+      }
+      const float m_new = fmaxf(m, warp_max(mixed));
+      const float p = live ? expf(mixed - m_new) : 0.f;
+      const float corr = m == -INFINITY ? 0.f : expf(m - m_new);
+      l = l * corr + warp_sum(p);
+      m = m_new;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) o[i] *= corr;
+      const int nk = min(PD_KEYS, k_end - k0);
+      for (int j = 0; j < nk; ++j) {
+        const float pj = __shfl_sync(0xffffffffu, p, j);
+        const int rj = __shfl_sync(0xffffffffu, row, j);
+        const TC* vr = vc + ((size_t)rj * G + kvh) * V;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int d = lane + 32 * i;
+          if (d < V) o[i] = fmaf(pj, ldf(vr + d), o[i]);
+        }
+      }
+    }
+  }
+  if (lane == 0) {
+    dst[0] = m;
+    dst[1] = l;
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int d = lane + 32 * i;
+    if (d < V) dst[2 + d] = o[i];
+  }
+}
+
+// folds the splits of every (row, head) in split order, divides, turns the sum back by the row's position, rounds; a CTA per row, a warp
+// per head at a time
+template <typename TX>
+__global__ void __launch_bounds__(128) premix_merge_kernel(const float* __restrict__ partial, int nsplit, HeadsGeom g, const int32_t* __restrict__ positions,
+                                                           const int32_t* __restrict__ seq_lens, TX* __restrict__ out) {
+  extern __shared__ float sm[];   // [4 warps][vdim]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int H = g.heads, V = g.vdim, vhalf = g.rot_values ? V / 2 : 0;
+  const bool empty = seq_lens[b] <= 0;
+  const int pos = positions[b];
+  float* row = sm + warp * V;
+  for (int h = warp; h < H; h += 4) {
+    TX* dst = out + ((size_t)b * H + h) * V;
+    if (empty) {
+      for (int d = lane; d < V; d += 32) stf(dst + d, 0.f);
+      continue;
+    }
+    const float* p = partial + ((size_t)b * nsplit * H + h) * (V + 2);
+    const size_t stride = (size_t)H * (V + 2);
+    float m = -INFINITY;
+    for (int s2 = 0; s2 < nsplit; ++s2) m = fmaxf(m, p[s2 * stride]);
+    float den = 0.f;
+    for (int s2 = 0; s2 < nsplit; ++s2) {
+      const float ms = p[s2 * stride];
+      den += ms == -INFINITY ? 0.f : p[s2 * stride + 1] * expf(ms - m);
+    }
+    const float inv = 1.0f / den;
+    for (int d = lane; d < V; d += 32) {
+      float acc = 0.f;
+      for (int s2 = 0; s2 < nsplit; ++s2) {
+        const float ms = p[s2 * stride];
+        if (ms != -INFINITY) acc = fmaf(p[s2 * stride + 2 + d], expf(ms - m), acc);
+      }
+      row[d] = acc * inv;
+    }
+    __syncwarp();
+    for (int d = lane; d < V; d += 32) {
+      float y = row[d];
+      if (d < 2 * vhalf) {
+        const int i = d < vhalf ? d : d - vhalf;
+        float c, sn;
+        pair_cos_sin(pos, i, V, g.rot_base, &c, &sn);
+        const float z = row[d < vhalf ? d + vhalf : d - vhalf];
+        y = d < vhalf ? y * c + z * sn : y * c - z * sn;
+      }
+      stf(dst + d, y);
+    }
+    __syncwarp();
+  }
+}
+
+int premix_decode_splits(int rows, int max_context) {
+  int ns = (2 * 148 + rows - 1) / std::max(rows, 1);   // about two CTAs per SM
+  ns = std::min(std::min(ns, 32), std::max(1, (max_context + 2 * PD_KEYS - 1) / (2 * PD_KEYS)));
+  return std::max(ns, 1);
+}
+
+template <typename TC, int NV>
+int launch_premix_decode_nv(const PremixDecodeArgs& a, int T, size_t smem, cudaStream_t s) {
+  static B2PerDeviceOnce once;
+  static size_t set_to = 0;
+  if (smem > 48 * 1024 && (once.need() || smem > set_to)) {
+    B2_CUDA_OK(cudaFuncSetAttribute(heads_attention_premix_decode_kernel<TC, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max(smem, set_to)));
+    set_to = std::max(smem, set_to);
+  }
+  B2_CUDA_OK(b2_launch(heads_attention_premix_decode_kernel<TC, NV>, dim3(T, a.nsplit), dim3(32 * a.g.heads), smem, s, a));
+  return 0;
+}
+template <typename TC>
+int launch_premix_decode_t(const PremixDecodeArgs& a, int T, size_t smem, cudaStream_t s) {
+  const int nv = (a.g.vdim + 31) / 32;
+  if (nv <= 1) return launch_premix_decode_nv<TC, 1>(a, T, smem, s);
+  if (nv <= 2) return launch_premix_decode_nv<TC, 2>(a, T, smem, s);
+  if (nv <= 4) return launch_premix_decode_nv<TC, 4>(a, T, smem, s);
+  if (nv <= 8) return launch_premix_decode_nv<TC, 8>(a, T, smem, s);
+  return launch_premix_decode_nv<TC, 16>(a, T, smem, s);
+}
+
 template <typename TC, typename TX>
 int launch_premix_t(const PremixArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
   static B2PerDeviceOnce once;
@@ -1280,7 +1494,8 @@ int launch_heads_finish_halves(const float* proj, int ld, const HeadsGeom& g, co
 
 int launch_heads_attention_premix(const float* q, const void* k_cache, const void* v_cache, int cache_f32, const HeadsGeom& g, const float* mix,
                                   const int32_t* block_table, int bt_stride, int block_size, const PrefillTile* tiles, int ntiles,
-                                  const int32_t* positions, const int32_t* seq_lens, void* out, int out_f32, int T, cudaStream_t s) {
+                                  const int32_t* positions, const int32_t* seq_lens, void* out, int out_f32, int T, cudaStream_t s, float* scratch,
+                                  size_t scratch_floats, int max_context) {
   if (T <= 0 || (tiles != nullptr && ntiles <= 0)) return 0;
   B2_REQUIRE(g.heads >= 1 && g.kv_heads >= 1 && g.heads % g.kv_heads == 0, "heads_attention_premix: %d heads over %d key/value heads", g.heads, g.kv_heads);
   B2_REQUIRE(cache_f32 == out_f32, "heads_attention_premix: cache and output have one element type");
@@ -1293,6 +1508,20 @@ int launch_heads_attention_premix(const float* q, const void* k_cache, const voi
     if (g.heads <= 8) return launch_premix_mma_h<8>(nu, a, grid, smem, s);
     if (g.heads <= 16) return launch_premix_mma_h<16>(nu, a, grid, smem, s);
     return launch_premix_mma_h<32>(nu, a, grid, smem, s);
+  }
+  if (tiles == nullptr && scratch != nullptr && g.heads <= 32 && g.vdim <= 512) {   // a decode step: key splits with a warp per head, then the merge
+    int ns = premix_decode_splits(T, max_context);
+    while (ns > 1 && (size_t)T * ns * g.heads * (g.vdim + 2) > scratch_floats) --ns;
+    const size_t smem = ((size_t)g.heads * (g.dim + PD_KEYS) + (size_t)g.heads * g.heads) * sizeof(float);
+    if ((size_t)T * ns * g.heads * (g.vdim + 2) <= scratch_floats && smem <= 200 * 1024) {
+      PremixDecodeArgs a{q, k_cache, v_cache, g, mix, block_table, bt_stride, block_size, positions, seq_lens, scratch, ns};
+      if (cache_f32) B2_TRY_RC(launch_premix_decode_t<float>(a, T, smem, s));
+      else B2_TRY_RC(launch_premix_decode_t<bf16>(a, T, smem, s));
+      const size_t msm = (size_t)4 * g.vdim * sizeof(float);
+      if (out_f32) B2_CUDA_OK(b2_launch(premix_merge_kernel<float>, dim3(T), dim3(128), msm, s, (const float*)scratch, ns, g, positions, seq_lens, (float*)out));
+      else B2_CUDA_OK(b2_launch(premix_merge_kernel<bf16>, dim3(T), dim3(128), msm, s, (const float*)scratch, ns, g, positions, seq_lens, (bf16*)out));
+      return 0;
+    }
   }
   // query tokens per CTA: as many as fit beside a second CTA on the SM, at least one
   int qt = tiles != nullptr ? 16 : 1;
@@ -1377,6 +1606,11 @@ int launch_heads_attention(const float* q, const void* k_cache, const void* v_ca
   if (out_f32)
     return launch_attention_t<bf16, float>(q, k_cache, v_cache, g, block_table, bt_stride, block_size, tiles, ntiles, positions, seq_lens, out, T, s);
   return launch_attention_t<bf16, bf16>(q, k_cache, v_cache, g, block_table, bt_stride, block_size, tiles, ntiles, positions, seq_lens, out, T, s);
+}
+
+size_t heads_attention_premix_scratch_floats(int max_rows, int heads, int vdim) {
+  // rows * splits stays below two CTAs per SM plus one split per row
+  return ((size_t)2 * 148 + 2 * (size_t)max_rows) * heads * ((size_t)vdim + 2);
 }
 
 int launch_talk_gate(const float* cross, const float* talk, const float* gate, int gate_ld, void* out, int out_f32, int heads, int kv_heads,

@@ -1563,7 +1563,8 @@ int forward_mixed_list(b2_engine* e, int T, int ntiles, int nlast) {
       {
         KL k(e, ntiles > 0 ? B2K_MISC : B2K_ATTN_DECODE);
         if (!k.skip()) B2_TRY(launch_heads_attention_premix(e->l_q, kc, vc, f, g, sp.score_mix ? L.talk : nullptr, e->d_block_table, e->bt_stride, c.block_size,
-                                                            tiles, ntiles, e->d_positions, e->d_seq_lens, e->l_av, f, T, st));
+                                                            tiles, ntiles, e->d_positions, e->d_seq_lens, e->l_av, f, T, st, e->l_attn_scratch,
+                                                            e->l_attn_scratch_floats, c.max_model_len));
       }
     } else {   // B2_MIXER_GATED_LATENT
       const LatentGeom g{sp.heads, sp.dim, 0, sp.vdim, sp.kv_rank, 0, 0.f, sp.scale, c.rms_eps, sp.window};
@@ -2997,15 +2998,19 @@ int mixed_engine_alloc(b2_engine* e) {
   B2_TRY(aalloc(&e->l_av, Tc * max_hv));
   B2_TRY(aalloc(&e->l_act, Tc * max_act));
   B2_TRY(aalloc(&e->l_xl, (size_t)e->l_rows_cap * W));
+  size_t scratch = 0;   // the key splits of a decode step's attention (one buffer: the layers run one after the other)
+  for (const ListLayer& L : e->ll)
+    if (L.sp.mixer == B2_MIXER_MIXED_SCORE_ATTENTION) scratch = std::max(scratch, heads_attention_premix_scratch_floats(bucket_batch(c.max_seqs), L.sp.heads, L.sp.vdim));
   if (any_latent) {
     B2_TRY(aalloc(&e->l_x2, Tc * max_qr));
     B2_TRY(aalloc(&e->l_qnope, Tc * max_hd));
     B2_TRY(dalloc(&e->l_qabs, Tc * max_hr));
     B2_TRY(aalloc(&e->l_olat, Tc * max_hr));
-    if (!e->f32) {
-      e->l_attn_scratch_floats = latent_attention_scratch_floats(bucket_batch(c.max_seqs), max_heads, max_rank);
-      B2_TRY(dalloc(&e->l_attn_scratch, e->l_attn_scratch_floats));
-    }
+    if (!e->f32) scratch = std::max(scratch, latent_attention_scratch_floats(bucket_batch(c.max_seqs), max_heads, max_rank));
+  }
+  if (scratch > 0) {
+    e->l_attn_scratch_floats = scratch;
+    B2_TRY(dalloc(&e->l_attn_scratch, scratch));
   }
   if (any_experts) {
     B2_TRY(dalloc(&e->l_y, Tc * max_top * W));

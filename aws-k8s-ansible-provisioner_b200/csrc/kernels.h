@@ -343,7 +343,11 @@ int launch_heads_finish_halves(const float* proj, int ld, const HeadsGeom& g, co
 // a query token are formed together.  tiles == null: decode form.  out [T][heads*vdim] (fp32 or bf16).
 int launch_heads_attention_premix(const float* q, const void* k_cache, const void* v_cache, int cache_f32, const HeadsGeom& g, const float* mix,
                                   const int32_t* block_table, int bt_stride, int block_size, const PrefillTile* tiles, int ntiles,
-                                  const int32_t* positions, const int32_t* seq_lens, void* out, int out_f32, int T, cudaStream_t s);
+                                  const int32_t* positions, const int32_t* seq_lens, void* out, int out_f32, int T, cudaStream_t s,
+                                  float* scratch = nullptr, size_t scratch_floats = 0, int max_context = 0);
+// scratch: device floats for the key splits of a decode step (heads_attention_premix_scratch_floats); without it a decode step runs unsplit,
+// a CTA per sequence.  max_context: the longest sequence the engine holds (bounds the number of splits).
+size_t heads_attention_premix_scratch_floats(int max_rows, int heads, int vdim);
 int launch_talk_gate(const float* cross, const float* talk, const float* gate, int gate_ld, void* out, int out_f32, int heads, int kv_heads,
                      int vdim, int T, cudaStream_t s);
 

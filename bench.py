@@ -479,8 +479,32 @@ def bumalix_model_cfg(width, heads, inter, layers=4, vocab=32000):
             "loop": {"start": 1, "stop": 3, "times": 1}, "layers": ls}
 
 
+# ---- --family tinevik: width, heads (128 wide, two per kv head), Qwen3's feed-forward width.  Four layers: gated linear attention (half as many heads,
+#      128 x 256), head-mixed softmax attention with rotated values (64 of 128 entries rotated, angles halved, cap 30), windowed latent attention (latent
+#      512, query latent width / 2, window 512), and the first layer's tensors once more; an xIELU feed-forward with Qwen3's parameter count in two
+#      matrices behind the state mixers, 16 table-routed clamped experts (two per token, Qwen3's active count) behind the others; vocab 32000.  The closest
+#      existing family is Bumalix (matrix states beside softmax attention, routed experts, an fp32 stream), which runs beside it at the same sizes.
+def tinevik_model_cfg(width, heads, inter, vocab=32000):
+    gla = {"heads": heads // 2, "dim": 128, "vdim": 256, "tau": 16.0}
+    att = {"heads": heads, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+           "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 2.0}}}
+    lat = {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": 512, "q_rank": width // 2, "scale": 128 ** -0.5, "mask": {"size": 512}}
+    dense = {"kind": "dense", "ff": min((3 * inter // 2 + 255) // 256 * 256, 16384)}
+    moe = {"kind": "moe", "expert": {"ff": (inter // 2 + 63) // 64 * 64, "limit": 7.0}, "router": {"experts": 16, "top": 2}}
+    ls = [{"type": "gla", "mixer": gla, "mlp": dense}, {"type": "attention", "mixer": att, "mlp": moe}, {"type": "latent_attention", "mixer": lat, "mlp": moe},
+          {"type": "gla", "mixer": gla, "mlp": dense, "weights_of": 0}]
+    return {"architecture": "Tinevik", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "logit_scale": 1.0, "norm": {"eps": 1e-6}, "layers": ls}
+
+
 def family_models(pkg, weights, family, tag):
     """(name, engine configuration, state-dict maker) of the family's model and of Qwen3 at the same width, depth, heads and feed-forward size."""
+    if family == "tinevik":
+        width, heads, inter = BUMALIX_SIZES[tag]
+        mc, bc = tinevik_model_cfg(width, heads, inter), bumalix_model_cfg(width, heads, inter)
+        return [("tinevik", pkg.EngineConfig.tinevik(mc), lambda c: weights.tinevik_random_state_dict(mc, seed=0, rank_a=16)),
+                ("bumalix", pkg.EngineConfig.bumalix(bc), lambda c: weights.bumalix_random_state_dict(bc, seed=0, rank_a=16, rank_g=16)),
+                ("qwen3", pkg.EngineConfig(num_layers=4, hidden=width, num_q_heads=heads, num_kv_heads=heads // 2, head_dim=128, intermediate=inter, vocab=32000),
+                 lambda c: weights.random_state_dict(c, seed=0))]
     if family == "bumalix":
         width, heads, inter = BUMALIX_SIZES[tag]
         mc = bumalix_model_cfg(width, heads, inter)
@@ -502,7 +526,7 @@ def family_models(pkg, weights, family, tag):
 
 
 def run_family(args, local):
-    """Prefill and decode throughput of a layer-list family (Lerasun, Kedasun, Bumalix) at layer sizes of real models (random weights), and of
+    """Prefill and decode throughput of a layer-list family (Lerasun, Kedasun, Bumalix, Tinevik) at layer sizes of real models (random weights), and of
     Qwen3 at the same width, depth, head count and (active) feed-forward size: one JSON line per size and model, with the decode step's
     per-kernel-class times (CUDA events around every launch of an eager step)."""
     import torch
@@ -557,7 +581,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--value-only", action="store_true", help="device-resident timing only (ablation runs)")
-    ap.add_argument("--family", default="", choices=["", "lerasun", "kedasun", "bumalix"],
+    ap.add_argument("--family", default="", choices=["", "lerasun", "kedasun", "bumalix", "tinevik"],
                     help="instead of the headline workload: the named family beside the closest GQA model at equal size (one GPU)")
     ap.add_argument("--family-sizes", default="w1024,w2048,w4096")
     ap.add_argument("--family-only", default="", help="time only the named model of the pair (the family's name, or qwen3)")
