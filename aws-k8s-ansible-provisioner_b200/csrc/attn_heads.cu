@@ -994,14 +994,14 @@ __global__ void __launch_bounds__(PM_WARPS * 32) heads_attention_premix_kernel(P
 }
 
 // ---- the same pass on warp-level tensor-core MMAs (bf16 caches, prompt portions, head sizes in multiples of 16) ----
-// One CTA of eight warps per 16 query tokens and ALL heads; keys go by in tiles of 64.  Per tile: for every key/value head its K rows are
-// staged (bf16) and the group's query heads form S = Q K^T, one 16 x 16 block per warp at a time, into an fp32 slab [heads][16][64]; then
-// every thread takes (token, key) pairs, reads the pair's scores of every head into registers (scale, cap), mixes them and writes them
-// back masked; then a warp per (token, head) row updates the row's maximum and sum and writes the weights as bf16; then for every
-// key/value head its V rows are staged and the warps accumulate P V into the output fragments they own (unit u = head * (vdim / 16) +
-// column block belongs to warp u mod 8), rescaled once per tile by the rows' factors.  The end goes through shared memory: division,
-// the turn back by the query's position (cosines and sines of the sixteen positions are formed once), rounding.
-constexpr int PX_ROWS = 16, PX_KEYS = 64, PX_THREADS = 256;
+// One CTA of eight warps per 16 query tokens and ALL heads; keys go by in tiles of 32.  Per tile: the K rows of every key/value head are
+// staged (bf16) and every query head forms S = Q K^T, one 16 x 16 block per warp at a time, into an fp32 slab [heads][16][32]; the V rows
+// take the K rows' place while every thread takes (token, key) pairs, reads the pair's scores of every head into registers (scale, cap),
+// mixes them and writes them back masked; then a warp per (token, head) row updates the row's maximum and sum and writes the weights as
+// bf16; then the warps accumulate P V into the output fragments they own (unit u = head * (vdim / 16) + column block belongs to warp
+// u mod 8), rescaled once per tile by the rows' factors.  The end goes through shared memory: division, the turn back by the query's
+// position (cosines and sines of the sixteen positions are formed once), rounding.
+constexpr int PX_ROWS = 16, PX_KEYS = 32, PX_THREADS = 256, PX_SLD = 36, PX_PLD = 40;
 struct PremixMmaArgs {
   const float* q;
   const bf16* k_cache;
@@ -1025,13 +1025,13 @@ __host__ __device__ inline PremixMmaLayout premix_mma_layout(const HeadsGeom& g)
   L.OP = V + 4;
   L.q_off = 0;
   L.k_off = L.q_off + (size_t)H * PX_ROWS * L.QP * 2;
-  L.s_off = L.k_off + (size_t)PX_KEYS * L.KP * 2;
-  L.p_off = L.s_off + (size_t)H * PX_ROWS * 68 * 4;
-  const size_t main_end = L.p_off + (size_t)H * PX_ROWS * 72 * 2;
+  L.s_off = L.k_off + (size_t)g.kv_heads * PX_KEYS * L.KP * 2;
+  L.p_off = L.s_off + (size_t)H * PX_ROWS * PX_SLD * 4;
+  const size_t main_end = L.p_off + (size_t)H * PX_ROWS * PX_PLD * 2;
   const size_t out_end = (size_t)H * PX_ROWS * L.OP * 4;              // the output slab reuses everything from the start
   L.misc_off = ((main_end > out_end ? main_end : out_end) + 127) / 128 * 128;
-  // misc: running maximum, sum, this tile's factor [heads * 16] each, the mixing matrix [heads * heads], positions [16], cache rows [64]
-  L.cs_off = L.misc_off + ((size_t)3 * H * PX_ROWS + (size_t)H * H + PX_ROWS + PX_KEYS) * 4;
+  // misc: running maximum, sum, this tile's factor [heads * 16] each, the mixing matrix [heads][up to 32], positions [16], cache rows [32]
+  L.cs_off = L.misc_off + ((size_t)3 * H * PX_ROWS + (size_t)H * 32 + PX_ROWS + PX_KEYS) * 4;
   L.total = L.cs_off + (size_t)PX_ROWS * V * 4;                        // cos [16][V/2] | sin [16][V/2]
   return L;
 }
@@ -1048,16 +1048,16 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
   const int H = g.heads, G = g.kv_heads, rep = H / G, D = g.dim, V = g.vdim, VB = V / 16;
   const PremixMmaLayout L = premix_mma_layout(g);
   bf16* Qs = reinterpret_cast<bf16*>(smraw + L.q_off);      // [H][16][QP]
-  bf16* Ks = reinterpret_cast<bf16*>(smraw + L.k_off);      // [64][KP]
-  float* Ss = reinterpret_cast<float*>(smraw + L.s_off);    // [H][16][68]
-  bf16* Ps = reinterpret_cast<bf16*>(smraw + L.p_off);      // [H][16][72]
+  bf16* Ks = reinterpret_cast<bf16*>(smraw + L.k_off);      // [G][32][KP]: the tile's K rows, then its V rows
+  float* Ss = reinterpret_cast<float*>(smraw + L.s_off);    // [H][16][36]
+  bf16* Ps = reinterpret_cast<bf16*>(smraw + L.p_off);      // [H][16][40]
   float* Os = reinterpret_cast<float*>(smraw);              // at the end: [H][16][OP]
   float* row_m = reinterpret_cast<float*>(smraw + L.misc_off);   // [H][16]
   float* row_l = row_m + H * PX_ROWS;
   float* row_f = row_l + H * PX_ROWS;
-  float* Tk = row_f + H * PX_ROWS;                          // [H][H]
-  int* row_pos = reinterpret_cast<int*>(Tk + H * H);        // [16]
-  int* key_row = row_pos + PX_ROWS;                         // [64]
+  float* Tk = row_f + H * PX_ROWS;                          // [H][HMAX]
+  int* row_pos = reinterpret_cast<int*>(Tk + H * HMAX);     // [16]
+  int* key_row = row_pos + PX_ROWS;                         // [32]
   float* cs = reinterpret_cast<float*>(smraw + L.cs_off);
 
   const PrefillTile tl = a.tiles[blockIdx.x];
@@ -1080,7 +1080,10 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
     row_m[i] = -INFINITY;
     row_l[i] = 0.f;
   }
-  for (int i = tid; i < H * H; i += PX_THREADS) Tk[i] = a.mix != nullptr ? a.mix[i] : ((i / H) == (i % H) ? 1.f : 0.f);
+  for (int i = tid; i < H * HMAX; i += PX_THREADS) {
+    const int h = i / HMAX, b = i - h * HMAX;
+    Tk[i] = b >= H ? 0.f : a.mix != nullptr ? a.mix[h * H + b] : (h == b ? 1.f : 0.f);
+  }
   if (tid < PX_ROWS) row_pos[tid] = tid < ntok ? pos_lo + tid : -1;
   // ---- which row of its 16 x 16 tile each accumulator element of this thread belongs to (the layout of a fragment is the compiler's
   //      business): read back from a tile that holds its own row numbers ----
@@ -1100,16 +1103,19 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
   for (int u = 0; u < NU; ++u) wmma::fill_fragment(oacc[u], 0.f);
   const int units = H * VB;
   const int32_t* bt = a.block_table + (size_t)tl.bt_row * a.bt_stride;
-  auto stage_rows = [&](const bf16* cache, int kvh, int width, int k0) {   // rows of one key/value head of the tile's keys, zeros past the last one
-    const int cpr = width / 8;   // 16-byte chunks per row
-    for (int idx = tid; idx < PX_KEYS * cpr; idx += PX_THREADS) {
-      const int j = idx / cpr, c = idx - j * cpr;
+  auto stage_rows = [&](const bf16* cache, int width) {   // the tile's rows of every key/value head, zeros past the last key
+    const int cpr = width / 8, per_key = G * cpr;   // 16-byte chunks per head row; a key's cache row holds the heads side by side
+#pragma unroll 4
+    for (int idx = tid; idx < PX_KEYS * per_key; idx += PX_THREADS) {
+      const int j = idx / per_key, rest = idx - j * per_key, kvh = rest / cpr, c = rest - kvh * cpr;
       const int kr = key_row[j];
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (kr >= 0) v = ld_stream(cache + ((size_t)kr * G + kvh) * width + c * 8);
-      *reinterpret_cast<uint4*>(Ks + (size_t)j * L.KP + c * 8) = v;
+      // asynchronous 16-byte copies (zero-filled past the last key): every chunk of a thread is in flight at once
+      const bf16* src = cache + (size_t)(kr >= 0 ? kr : 0) * G * width + (size_t)rest * 8;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(Ks + ((size_t)kvh * PX_KEYS + j) * L.KP + c * 8)), "l"(src), "r"(kr >= 0 ? 16 : 0));
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
+  auto stage_wait = [&]() { asm volatile("cp.async.wait_group 0;" ::: "memory"); };
   const int k_first = g.window > 0 ? max(0, pos_lo - g.window + 1) / PX_KEYS * PX_KEYS : 0;
   for (int k0 = k_first; k0 <= pos_hi; k0 += PX_KEYS) {
     __syncthreads();   // the tile before is consumed
@@ -1117,57 +1123,71 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
       const int kp = k0 + tid;
       key_row[tid] = kp <= pos_hi ? bt[kp / a.block_size] * a.block_size + kp % a.block_size : -1;
     }
-    // ---- S = Q K^T, key/value head by key/value head ----
-    for (int kvh = 0; kvh < G; ++kvh) {
-      __syncthreads();
-      stage_rows(a.k_cache, kvh, D, k0);
-      __syncthreads();
-      for (int u = warp; u < rep * 4; u += 8) {
-        const int h = kvh * rep + (u >> 2), kb = u & 3;
-        wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
-        wmma::fill_fragment(acc, 0.f);
-        for (int d = 0; d < D; d += 16) {
-          wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fq;
-          wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> fk;
-          wmma::load_matrix_sync(fq, Qs + (size_t)h * PX_ROWS * L.QP + d, L.QP);
-          wmma::load_matrix_sync(fk, Ks + (size_t)(16 * kb) * L.KP + d, L.KP);
-          wmma::mma_sync(acc, fq, fk, acc);
-        }
-        wmma::store_matrix_sync(Ss + (size_t)h * PX_ROWS * 68 + 16 * kb, acc, 68, wmma::mem_row_major);
+    __syncthreads();
+    stage_rows(a.k_cache, D);
+    stage_wait();
+    __syncthreads();
+    // ---- S = Q K^T: unit u = head * 2 + key block ----
+    for (int u = warp; u < H * 2; u += 8) {
+      const int h = u >> 1, kb = u & 1;
+      wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+      wmma::fill_fragment(acc, 0.f);
+      const bf16* kbase = Ks + ((size_t)(h / rep) * PX_KEYS + 16 * kb) * L.KP;
+      for (int d = 0; d < D; d += 16) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fq;
+        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> fk;
+        wmma::load_matrix_sync(fq, Qs + (size_t)h * PX_ROWS * L.QP + d, L.QP);
+        wmma::load_matrix_sync(fk, kbase + d, L.KP);
+        wmma::mma_sync(acc, fq, fk, acc);
       }
+      wmma::store_matrix_sync(Ss + (size_t)h * PX_ROWS * PX_SLD + 16 * kb, acc, PX_SLD, wmma::mem_row_major);
     }
     __syncthreads();
-    // ---- scale, cap, mix over the heads, mask: a thread per (token, key) pair, the pair's scores of every head in registers ----
-    for (int idx = tid; idx < PX_ROWS * PX_KEYS; idx += PX_THREADS) {
-      const int r = idx >> 6, j = idx & 63;
-      const int pos = row_pos[r], kp = k0 + j;
-      const bool vis = kp <= pos && (g.window <= 0 || pos - kp < g.window);
-      float sc[HMAX];
+    stage_rows(a.v_cache, V);   // (the K rows are consumed; the loads fly while the scores are mixed)
+    // ---- scale, cap, mix over the heads, mask: a thread takes the (token, key) pairs (r, j) and (r + 8, j) and holds both pairs' scores
+    //      of every head in registers, so that a row of the mixing matrix is read once (four entries a load) for both ----
+    {
+      const int r0 = tid >> 5, j = tid & 31, kp = k0 + j;
+      float sc[2][HMAX];
 #pragma unroll
-      for (int b = 0; b < HMAX; ++b)
-        if (b < H) {
-          float v = Ss[((size_t)b * PX_ROWS + r) * 68 + j] * g.scale;
-          if (g.softcap > 0.f) v = g.softcap * tanhf(v / g.softcap);
-          sc[b] = v;
+      for (int x = 0; x < 2; ++x)
+#pragma unroll
+        for (int b = 0; b < HMAX; ++b) {
+          float v = 0.f;
+          if (b < H) {
+            v = Ss[((size_t)b * PX_ROWS + r0 + 8 * x) * PX_SLD + j] * g.scale;
+            // cap * tanh(v / cap) as cap * (1 - 2 / (exp(2 v / cap) + 1)): the operands of this kernel are bf16, its fast exponential is not what bounds it
+            if (g.softcap > 0.f) v = g.softcap * (1.0f - __fdividef(2.0f, __expf(2.0f * v / g.softcap) + 1.0f));
+          }
+          sc[x][b] = v;
         }
+      const int p0 = row_pos[r0], p1 = row_pos[r0 + 8];
+      const bool vis0 = kp <= p0 && (g.window <= 0 || p0 - kp < g.window), vis1 = kp <= p1 && (g.window <= 0 || p1 - kp < g.window);
       for (int h = 0; h < H; ++h) {
-        float acc = 0.f;
+        float a0 = 0.f, a1 = 0.f;
+        const float* trow = Tk + h * HMAX;   // (rows padded to HMAX entries, zeros behind the heads)
 #pragma unroll
-        for (int b = 0; b < HMAX; ++b)
-          if (b < H) acc = fmaf(Tk[h * H + b], sc[b], acc);
-        Ss[((size_t)h * PX_ROWS + r) * 68 + j] = vis ? acc : -INFINITY;
+        for (int b = 0; b < HMAX; b += 4) {
+          const float4 t4 = *reinterpret_cast<const float4*>(trow + b);
+          a0 = fmaf(t4.x, sc[0][b], a0); a1 = fmaf(t4.x, sc[1][b], a1);
+          a0 = fmaf(t4.y, sc[0][b + 1], a0); a1 = fmaf(t4.y, sc[1][b + 1], a1);
+          a0 = fmaf(t4.z, sc[0][b + 2], a0); a1 = fmaf(t4.z, sc[1][b + 2], a1);
+          a0 = fmaf(t4.w, sc[0][b + 3], a0); a1 = fmaf(t4.w, sc[1][b + 3], a1);
+        }
+        Ss[((size_t)h * PX_ROWS + r0) * PX_SLD + j] = vis0 ? a0 : -INFINITY;
+        Ss[((size_t)h * PX_ROWS + r0 + 8) * PX_SLD + j] = vis1 ? a1 : -INFINITY;
       }
     }
+    stage_wait();   // this thread's V chunks have landed
     __syncthreads();
     // ---- a warp per (head, token) row: maximum, weights (bf16: what is summed is what multiplies the values), sum, this tile's factor ----
     for (int row = warp; row < H * PX_ROWS; row += 8) {
-      const float s0 = Ss[(size_t)row * 68 + lane], s1 = Ss[(size_t)row * 68 + 32 + lane];
+      const float s0 = Ss[(size_t)row * PX_SLD + lane];
       const float m_old = row_m[row];
-      const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
-      const bf16 p0 = __float2bfloat16_rn(s0 == -INFINITY ? 0.f : expf(s0 - m_new)), p1 = __float2bfloat16_rn(s1 == -INFINITY ? 0.f : expf(s1 - m_new));
-      Ps[(size_t)row * 72 + lane] = p0;
-      Ps[(size_t)row * 72 + 32 + lane] = p1;
-      const float psum = warp_sum(__bfloat162float(p0) + __bfloat162float(p1));
+      const float m_new = fmaxf(m_old, warp_max(s0));
+      const bf16 p0 = __float2bfloat16_rn(s0 == -INFINITY ? 0.f : expf(s0 - m_new));
+      Ps[(size_t)row * PX_PLD + lane] = p0;
+      const float psum = warp_sum(__bfloat162float(p0));
       if (lane == 0) {
         const float corr = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
         row_m[row] = m_new;
@@ -1175,26 +1195,23 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
         row_f[row] = corr;
       }
     }
-    // ---- O = O * factor + P V, key/value head by key/value head ----
-    for (int kvh = 0; kvh < G; ++kvh) {
-      __syncthreads();   // (first time: weights and factors are written)
-      stage_rows(a.v_cache, kvh, V, k0);
-      __syncthreads();
+    __syncthreads();   // weights, factors and the V rows are in place
+    // ---- O = O * factor + P V ----
 #pragma unroll
-      for (int i = 0; i < NU; ++i) {
-        const int u = warp + 8 * i;
-        if (u >= units) continue;
-        const int h = u / VB, cb = u - h * VB;
-        if (h / rep != kvh) continue;
+    for (int i = 0; i < NU; ++i) {
+      const int u = warp + 8 * i;
+      if (u >= units) continue;
+      const int h = u / VB, cb = u - h * VB;
 #pragma unroll
-        for (int e = 0; e < NE; ++e) oacc[i].x[e] *= row_f[h * PX_ROWS + frag_row[e]];
-        for (int kk = 0; kk < PX_KEYS; kk += 16) {
-          wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fp;
-          wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> fv;
-          wmma::load_matrix_sync(fp, Ps + (size_t)h * PX_ROWS * 72 + kk, 72);
-          wmma::load_matrix_sync(fv, Ks + (size_t)kk * L.KP + 16 * cb, L.KP);
-          wmma::mma_sync(oacc[i], fp, fv, oacc[i]);
-        }
+      for (int e = 0; e < NE; ++e) oacc[i].x[e] *= row_f[h * PX_ROWS + frag_row[e]];
+      const bf16* vbase = Ks + (size_t)(h / rep) * PX_KEYS * L.KP + 16 * cb;
+#pragma unroll
+      for (int kk = 0; kk < PX_KEYS; kk += 16) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fp;
+        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> fv;
+        wmma::load_matrix_sync(fp, Ps + (size_t)h * PX_ROWS * PX_PLD + kk, PX_PLD);
+        wmma::load_matrix_sync(fv, vbase + (size_t)kk * L.KP, L.KP);
+        wmma::mma_sync(oacc[i], fp, fv, oacc[i]);
       }
     }
   }
