@@ -1401,18 +1401,23 @@ __global__ void __launch_bounds__(1024) heads_attention_premix_decode_kernel(Pre
 }
 
 // folds the splits of every (row, head) in split order, divides, turns the sum back by the row's position, rounds; a CTA per row, a warp
-// per head at a time
+// per head at a time (lane s holds split s: at most 32 splits); the row's cosines and sines are formed once for all heads
 template <typename TX>
 __global__ void __launch_bounds__(128) premix_merge_kernel(const float* __restrict__ partial, int nsplit, HeadsGeom g, const int32_t* __restrict__ positions,
                                                            const int32_t* __restrict__ seq_lens, TX* __restrict__ out) {
-  extern __shared__ float sm[];   // [4 warps][vdim]
+  extern __shared__ float sm[];   // [4 warps][vdim], then cos [vdim/2] | sin [vdim/2]
   pdl_wait();
   pdl_launch_dependents();
   const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int H = g.heads, V = g.vdim, vhalf = g.rot_values ? V / 2 : 0;
   const bool empty = seq_lens[b] <= 0;
-  const int pos = positions[b];
   float* row = sm + warp * V;
+  float* cs = sm + 4 * V;
+  if (!empty) {
+    const int pos = positions[b];
+    for (int i = threadIdx.x; i < vhalf; i += 128) pair_cos_sin(pos, i, V, g.rot_base, &cs[i], &cs[vhalf + i]);
+  }
+  __syncthreads();
   for (int h = warp; h < H; h += 4) {
     TX* dst = out + ((size_t)b * H + h) * V;
     if (empty) {
@@ -1421,31 +1426,27 @@ __global__ void __launch_bounds__(128) premix_merge_kernel(const float* __restri
     }
     const float* p = partial + ((size_t)b * nsplit * H + h) * (V + 2);
     const size_t stride = (size_t)H * (V + 2);
-    float m = -INFINITY;
-    for (int s2 = 0; s2 < nsplit; ++s2) m = fmaxf(m, p[s2 * stride]);
-    float den = 0.f;
-    for (int s2 = 0; s2 < nsplit; ++s2) {
-      const float ms = p[s2 * stride];
-      den += ms == -INFINITY ? 0.f : p[s2 * stride + 1] * expf(ms - m);
-    }
-    const float inv = 1.0f / den;
-    for (int d = lane; d < V; d += 32) {
+    const float ms = lane < nsplit ? p[lane * stride] : -INFINITY;
+    const float ls = lane < nsplit ? p[lane * stride + 1] : 0.f;
+    const float m = warp_max(ms);
+    const float wgt = ms == -INFINITY ? 0.f : expf(ms - m);
+    const float inv = 1.0f / warp_sum(ls * wgt);
+    for (int d0 = 0; d0 < V; d0 += 32) {
+      const int d = d0 + lane;
       float acc = 0.f;
       for (int s2 = 0; s2 < nsplit; ++s2) {
-        const float ms = p[s2 * stride];
-        if (ms != -INFINITY) acc = fmaf(p[s2 * stride + 2 + d], expf(ms - m), acc);
+        const float w2 = __shfl_sync(0xffffffffu, wgt, s2);
+        if (d < V && w2 != 0.f) acc = fmaf(p[s2 * stride + 2 + d], w2, acc);
       }
-      row[d] = acc * inv;
+      if (d < V) row[d] = acc * inv;
     }
     __syncwarp();
     for (int d = lane; d < V; d += 32) {
       float y = row[d];
       if (d < 2 * vhalf) {
         const int i = d < vhalf ? d : d - vhalf;
-        float c, sn;
-        pair_cos_sin(pos, i, V, g.rot_base, &c, &sn);
         const float z = row[d < vhalf ? d + vhalf : d - vhalf];
-        y = d < vhalf ? y * c + z * sn : y * c - z * sn;
+        y = d < vhalf ? y * cs[i] + z * cs[vhalf + i] : y * cs[i] - z * cs[vhalf + i];
       }
       stf(dst + d, y);
     }
@@ -1534,7 +1535,7 @@ int launch_heads_attention_premix(const float* q, const void* k_cache, const voi
       PremixDecodeArgs a{q, k_cache, v_cache, g, mix, block_table, bt_stride, block_size, positions, seq_lens, scratch, ns};
       if (cache_f32) B2_TRY_RC(launch_premix_decode_t<float>(a, T, smem, s));
       else B2_TRY_RC(launch_premix_decode_t<bf16>(a, T, smem, s));
-      const size_t msm = (size_t)4 * g.vdim * sizeof(float);
+      const size_t msm = (size_t)5 * g.vdim * sizeof(float);
       if (out_f32) B2_CUDA_OK(b2_launch(premix_merge_kernel<float>, dim3(T), dim3(128), msm, s, (const float*)scratch, ns, g, positions, seq_lens, (float*)out));
       else B2_CUDA_OK(b2_launch(premix_merge_kernel<bf16>, dim3(T), dim3(128), msm, s, (const float*)scratch, ns, g, positions, seq_lens, (bf16*)out));
       return 0;

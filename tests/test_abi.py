@@ -40,9 +40,10 @@ def test_config_struct_layout(pkg):
     from importlib import import_module
     capi = import_module("aws-k8s-ansible-provisioner_b200.capi")
     # 18 four-byte fields + one pointer + 4 four-byte fields (arch, rotary_dim, max_positions, sliding_window)
-    # + ABI v3: the layer list pointer, compute_f32, logit_scale; v4: embed_scale, norm_groups; v5: the loop's three fields, logit_softcap
-    assert C.sizeof(capi.b2_config) == 18 * 4 + 8 + 4 * 4 + 8 + 4 * 4 + 4 * 4
-    assert C.sizeof(capi.b2_layer_spec) == 27 * 4
+    # + ABI v3: the layer list pointer, compute_f32, logit_scale; v4: embed_scale, norm_groups; v5: the loop's three fields, logit_softcap;
+    # v6: norm_kind (and four bytes of padding behind it: the struct holds pointers)
+    assert C.sizeof(capi.b2_config) == 18 * 4 + 8 + 4 * 4 + 8 + 4 * 4 + 4 * 4 + 8
+    assert C.sizeof(capi.b2_layer_spec) == 33 * 4
     assert capi.b2_config.arch.offset == 18 * 4 + 8 and capi.b2_config.rotary_dim.offset == 18 * 4 + 12
     assert C.sizeof(capi.b2_sampling) == 24
 

@@ -456,3 +456,107 @@ def test_greedy_generation_through_the_server(tmp_path):
             proc.wait(timeout=10)
         except Exception:
             proc.kill()
+
+
+def random_model(seed):
+    """A random layer list: every mixer and feed-forward kind in a random order, sizes drawn per layer, some layers running with an earlier
+    layer's tensors."""
+    rng = np.random.RandomState(seed)
+    pick = lambda xs: xs[rng.randint(len(xs))]
+    layers = []
+    for i in range(int(rng.randint(3, 7))):
+        if i >= 2 and rng.rand() < 0.3:
+            j = int(rng.randint(0, i))
+            while len(layers[j]) > 2:
+                j = layers[j][2]
+            layers.append((layers[j][0], layers[j][1], j))
+            continue
+        kind = pick(["gla", "attention", "latent"])
+        if kind == "gla":
+            m = gla(pick([1, 2, 3]), pick([6, 8, 20]), pick([4, 10, 36]), pick([1.0, 4.0, 16.0]), rank=pick([1, 3, 5]))
+        elif kind == "attention":
+            kv = pick([1, 2, 3])
+            d, dv = pick([6, 8, 16, 22]), pick([4, 8, 16, 18])
+            rot = pick([None, (pick([100.0, 1e4, 2.5e5]), pick([2, d - d % 2, 4]), pick([None, 2.0, 8.0]))])
+            m = att(kv * pick([1, 2, 4]), kv, d, dv, pick([0.2, 0.35]), rot=rot, cap=pick([None, 6.0, 30.0]))
+        else:
+            m = lat(pick([1, 2, 5]), pick([4, 8, 12]), pick([4, 8, 14]), pick([6, 16, 24]), pick([5, 8, 16]), pick([0.3, 0.5]), window=pick([None, 1, 7, 16, 33]))
+        f = pick([None, dense(pick([8, 24, 50])), moe(pick([1, 3, 8]), 1, pick([6, 16])), moe(pick([4, 6]), pick([2, 4]), pick([6, 10]))])
+        layers.append((m, f))
+    return model(layers, vocab=int(pick([53, 160, 301])), width=int(pick([24, 40, 56, 72])), escale=float(pick([1.0, 4.0, 16.0])),
+                 eps=float(pick([1e-6, 1e-5])), lscale=float(pick([1.0, 2.0])))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_models_and_schedules(seed):
+    """Up to four live requests over a pool that holds only what is live: portions of some beside single tokens of others, requests that end
+    and give their pages and slots to the next, in fp32 and (even seeds) in bf16."""
+    cfg = random_model(seed)
+    w = random_weights(cfg, seed=50 + seed)
+    rng = np.random.RandomState(1000 + seed)
+    f32 = seed % 2 == 1
+    bar = F32_BAR if f32 else 4 * BF16_BAR
+    lens = [int(rng.randint(1, 130)) for _ in range(7)]
+    prompts = [tokens(cfg, n, 2000 + 10 * seed + i) for i, n in enumerate(lens)]
+    refs = [ref_logits(cfg, w, p) for p in prompts]
+    with engine(cfg, w, f32=f32, num_blocks=4 * 9 + 1, max_seqs=4, max_model_len=144, max_batch_tokens=576) as e:
+        live, done, nxt, sid = [], {}, 0, {}
+        worst = []
+        while nxt < len(prompts) or live:
+            while len(live) < 4 and nxt < len(prompts) and (not live or rng.rand() < 0.6):
+                sid[nxt] = e.seq_create(1)
+                done[nxt] = 0
+                live.append(nxt)
+                nxt += 1
+            step = [r for r in live if rng.rand() < 0.8] or live[:1]
+            sizes = {r: min(len(prompts[r]) - done[r], int(pick_size(rng))) for r in step}
+            for r in step:
+                e.seq_reserve(sid[r], done[r] + sizes[r])
+            if all(sizes[r] == 1 and done[r] >= 1 for r in step):
+                e.decode_step([sid[r] for r in step], in_tokens=[prompts[r][done[r]] for r in step], want_output=False)
+                lg = e.get_logits(len(step))
+                got = {r: lg[k:k + 1] for k, r in enumerate(step)}
+            else:
+                chunks = [prompts[r][done[r]:done[r] + sizes[r]] for r in step]
+                lg, _ = e.prefill_logits([sid[r] for r in step], chunks, list(range(sum(sizes.values()))))
+                got, base = {}, 0
+                for r in step:
+                    got[r] = lg[base:base + sizes[r]]
+                    base += sizes[r]
+            for r in step:
+                worst.append(err(got[r], refs[r][done[r]:done[r] + sizes[r]]))
+                done[r] += sizes[r]
+                if done[r] == len(prompts[r]):
+                    e.seq_free(sid[r])
+                    live.remove(r)
+        worst = np.array(worst)
+        if f32:
+            assert worst.max() < bar, (cfg, worst.max())
+        else:    # a bf16 product rounds its operands: the bulk is barred tightly, the worst loosely
+            assert np.median(worst) < BF16_BAR and worst.max() < bar, (cfg, np.median(worst), worst.max())
+
+
+def pick_size(rng):
+    return [1, 1, 1, 2, 2, 3, 16, 17, 40, 64, 100][rng.randint(11)]
+
+
+def test_a_trace_replayed_through_the_command_line(tmp_path):
+    """bin/trace_run: steps on standard input, the logits asked for as files, a pool sized for the live tokens only."""
+    cfg = cfg_a()
+    w = random_weights(cfg, seed=31)
+    a, b = tokens(cfg, 90, 32), tokens(cfg, 21, 33)
+    ra, rb = ref_logits(cfg, w, a), ref_logits(cfg, w, b)
+    mdir, out = write_dir(cfg, w, tmp_path / "m"), tmp_path / "out"
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:70], "want": [0, 69]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[70:72], "want": []}, {"id": "b", "tokens": b[:20], "want": [19]}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[72:73], "want": [0]}, {"id": "b", "tokens": b[20:], "want": [0]}], "end": ["b"]},
+             {"step": 3, "entries": [{"id": "a", "tokens": a[73:], "want": [16]}], "end": ["a"]},
+             {"step": 4, "entries": [{"id": "c", "tokens": b, "want": [20]}], "end": ["c"]}]
+    exe = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bin", "trace_run")
+    r = subprocess.run([exe, "--model", mdir, "--dtype", "float32", "--out", str(out), "--max-tokens", "192"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    assert [l for l in r.stdout.split("\n") if l.startswith("done")] == ["done %d" % i for i in range(5)]
+    rd = lambda i: np.fromfile(str(out / ("%d.f32" % i)), dtype="<f4").reshape(-1, cfg["vocab"])
+    assert err(rd(0), ra[[0, 69]]) < F32_BAR and err(rd(1), rb[[19]]) < F32_BAR
+    assert err(rd(2), np.stack([ra[72], rb[20]])) < F32_BAR and err(rd(3), ra[[89]]) < F32_BAR and err(rd(4), rb[[20]]) < F32_BAR
