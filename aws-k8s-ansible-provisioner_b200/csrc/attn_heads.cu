@@ -994,14 +994,14 @@ __global__ void __launch_bounds__(PM_WARPS * 32) heads_attention_premix_kernel(P
 }
 
 // ---- the same pass on warp-level tensor-core MMAs (bf16 caches, prompt portions, head sizes in multiples of 16) ----
-// One CTA of eight warps per 16 query tokens and ALL heads; keys go by in tiles of 32.  Per tile: the K rows of every key/value head are
+// One CTA of sixteen warps per 16 query tokens and ALL heads; keys go by in tiles of 32.  Per tile: the K rows of every key/value head are
 // staged (bf16) and every query head forms S = Q K^T, one 16 x 16 block per warp at a time, into an fp32 slab [heads][16][32]; the V rows
-// take the K rows' place while every thread takes (token, key) pairs, reads the pair's scores of every head into registers (scale, cap),
-// mixes them and writes them back masked; then a warp per (token, head) row updates the row's maximum and sum and writes the weights as
-// bf16; then the warps accumulate P V into the output fragments they own (unit u = head * (vdim / 16) + column block belongs to warp
-// u mod 8), rescaled once per tile by the rows' factors.  The end goes through shared memory: division, the turn back by the query's
+// take the K rows' place while every thread takes one (token, key) pair, reads the pair's scores of every head into registers (scale, cap),
+// mixes them (two heads per packed fp32 multiply-add, each head's sum in the order of the heads) and writes them back masked; then two
+// threads per (token, head) row update the row's maximum and sum and write the weights as bf16; then the warps accumulate P V into the
+// output fragments they own (unit u = head * (vdim / 16) + column block belongs to warp u mod 16), rescaled once per tile by the rows' factors.  The end goes through shared memory: division, the turn back by the query's
 // position (cosines and sines of the sixteen positions are formed once), rounding.
-constexpr int PX_ROWS = 16, PX_KEYS = 32, PX_THREADS = 256, PX_SLD = 36, PX_PLD = 40;
+constexpr int PX_ROWS = 16, PX_KEYS = 32, PX_WARPS = 16, PX_THREADS = 32 * PX_WARPS, PX_SLD = 36, PX_PLD = 40;
 struct PremixMmaArgs {
   const float* q;
   const bf16* k_cache;
@@ -1036,7 +1036,7 @@ __host__ __device__ inline PremixMmaLayout premix_mma_layout(const HeadsGeom& g)
   return L;
 }
 
-// HMAX: register slots for one pair's scores (heads <= HMAX); NU: output fragments per warp (heads * vdim / 16 <= 8 * NU)
+// HMAX: register slots for one pair's scores (heads <= HMAX); NU: output fragments per warp (heads * vdim / 16 <= PX_WARPS * NU)
 template <int HMAX, int NU>
 __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kernel(PremixMmaArgs a) {
   using namespace nvcuda;
@@ -1055,7 +1055,7 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
   float* row_m = reinterpret_cast<float*>(smraw + L.misc_off);   // [H][16]
   float* row_l = row_m + H * PX_ROWS;
   float* row_f = row_l + H * PX_ROWS;
-  float* Tk = row_f + H * PX_ROWS;                          // [H][HMAX]
+  float* Tk = row_f + H * PX_ROWS;                          // [H][HMAX], transposed: entry [b][h] weighs head b's score in head h's mix
   int* row_pos = reinterpret_cast<int*>(Tk + H * HMAX);     // [16]
   int* key_row = row_pos + PX_ROWS;                         // [32]
   float* cs = reinterpret_cast<float*>(smraw + L.cs_off);
@@ -1081,8 +1081,8 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
     row_l[i] = 0.f;
   }
   for (int i = tid; i < H * HMAX; i += PX_THREADS) {
-    const int h = i / HMAX, b = i - h * HMAX;
-    Tk[i] = b >= H ? 0.f : a.mix != nullptr ? a.mix[h * H + b] : (h == b ? 1.f : 0.f);
+    const int b = i / HMAX, h = i - b * HMAX;
+    Tk[i] = h >= H ? 0.f : a.mix != nullptr ? a.mix[h * H + b] : (h == b ? 1.f : 0.f);
   }
   if (tid < PX_ROWS) row_pos[tid] = tid < ntok ? pos_lo + tid : -1;
   // ---- which row of its 16 x 16 tile each accumulator element of this thread belongs to (the layout of a fragment is the compiler's
@@ -1093,7 +1093,7 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
   int frag_row[NE];
   {
     __syncthreads();
-    Ss[tid] = (float)(tid >> 4);   // 256 threads: a 16 x 16 tile, row-major
+    if (tid < 256) Ss[tid] = (float)(tid >> 4);   // a 16 x 16 tile, row-major
     __syncthreads();
     wmma::load_matrix_sync(oacc[0], Ss, 16, wmma::mem_row_major);
 #pragma unroll
@@ -1128,7 +1128,7 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
     stage_wait();
     __syncthreads();
     // ---- S = Q K^T: unit u = head * 2 + key block ----
-    for (int u = warp; u < H * 2; u += 8) {
+    for (int u = warp; u < H * 2; u += PX_WARPS) {
       const int h = u >> 1, kb = u & 1;
       wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
       wmma::fill_fragment(acc, 0.f);
@@ -1144,44 +1144,45 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
     }
     __syncthreads();
     stage_rows(a.v_cache, V);   // (the K rows are consumed; the loads fly while the scores are mixed)
-    // ---- scale, cap, mix over the heads, mask: a thread takes the (token, key) pairs (r, j) and (r + 8, j) and holds both pairs' scores
-    //      of every head in registers, so that a row of the mixing matrix is read once (four entries a load) for both ----
+    // ---- scale, cap, mix over the heads, mask: a thread takes ONE (token, key) pair.  It walks the heads b in their order, reads the pair's
+    //      score of head b (scale, cap) and adds its share to the mixed score of every head h, two heads per packed fp32 multiply-add with
+    //      the matrix column b read four entries a load; every sum therefore runs over b upwards, as the plain kernel's does ----
     {
       const int r0 = tid >> 5, j = tid & 31, kp = k0 + j;
-      float sc[2][HMAX];
+      unsigned long long mixed[HMAX / 2];
 #pragma unroll
-      for (int x = 0; x < 2; ++x)
+      for (int h2 = 0; h2 < HMAX / 2; ++h2) mixed[h2] = 0ull;
+      const float* scol = Ss + (size_t)r0 * PX_SLD + j;
+#pragma unroll 4
+      for (int b = 0; b < H; ++b) {
+        float v = scol[(size_t)b * PX_ROWS * PX_SLD] * g.scale;
+        // cap * tanh(v / cap) as cap * (1 - 2 / (exp(2 v / cap) + 1)): the operands of this kernel are bf16, its fast exponential is not what bounds it
+        if (g.softcap > 0.f) v = g.softcap * (1.0f - __fdividef(2.0f, __expf(2.0f * v / g.softcap) + 1.0f));
+        unsigned long long vv;
+        asm("mov.b64 %0, {%1, %1};" : "=l"(vv) : "f"(v));
+        const float* tcol = Tk + b * HMAX;   // (padded to HMAX entries, zeros behind the heads)
 #pragma unroll
-        for (int b = 0; b < HMAX; ++b) {
-          float v = 0.f;
-          if (b < H) {
-            v = Ss[((size_t)b * PX_ROWS + r0 + 8 * x) * PX_SLD + j] * g.scale;
-            // cap * tanh(v / cap) as cap * (1 - 2 / (exp(2 v / cap) + 1)): the operands of this kernel are bf16, its fast exponential is not what bounds it
-            if (g.softcap > 0.f) v = g.softcap * (1.0f - __fdividef(2.0f, __expf(2.0f * v / g.softcap) + 1.0f));
-          }
-          sc[x][b] = v;
+        for (int h4 = 0; h4 < HMAX / 4; ++h4) {
+          const ulonglong2 t4 = *reinterpret_cast<const ulonglong2*>(tcol + 4 * h4);
+          asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(mixed[2 * h4]) : "l"(t4.x), "l"(vv));
+          asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(mixed[2 * h4 + 1]) : "l"(t4.y), "l"(vv));
         }
-      const int p0 = row_pos[r0], p1 = row_pos[r0 + 8];
-      const bool vis0 = kp <= p0 && (g.window <= 0 || p0 - kp < g.window), vis1 = kp <= p1 && (g.window <= 0 || p1 - kp < g.window);
-      for (int h = 0; h < H; ++h) {
-        float a0 = 0.f, a1 = 0.f;
-        const float* trow = Tk + h * HMAX;   // (rows padded to HMAX entries, zeros behind the heads)
+      }
+      const int p0 = row_pos[r0];
+      const bool vis = kp <= p0 && (g.window <= 0 || p0 - kp < g.window);
+      float* dcol = Ss + (size_t)r0 * PX_SLD + j;
 #pragma unroll
-        for (int b = 0; b < HMAX; b += 4) {
-          const float4 t4 = *reinterpret_cast<const float4*>(trow + b);
-          a0 = fmaf(t4.x, sc[0][b], a0); a1 = fmaf(t4.x, sc[1][b], a1);
-          a0 = fmaf(t4.y, sc[0][b + 1], a0); a1 = fmaf(t4.y, sc[1][b + 1], a1);
-          a0 = fmaf(t4.z, sc[0][b + 2], a0); a1 = fmaf(t4.z, sc[1][b + 2], a1);
-          a0 = fmaf(t4.w, sc[0][b + 3], a0); a1 = fmaf(t4.w, sc[1][b + 3], a1);
-        }
-        Ss[((size_t)h * PX_ROWS + r0) * PX_SLD + j] = vis0 ? a0 : -INFINITY;
-        Ss[((size_t)h * PX_ROWS + r0 + 8) * PX_SLD + j] = vis1 ? a1 : -INFINITY;
+      for (int h2 = 0; h2 < HMAX / 2; ++h2) {
+        float lo, hi;
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(mixed[h2]));
+        if (2 * h2 < H) dcol[(size_t)(2 * h2) * PX_ROWS * PX_SLD] = vis ? lo : -INFINITY;
+        if (2 * h2 + 1 < H) dcol[(size_t)(2 * h2 + 1) * PX_ROWS * PX_SLD] = vis ? hi : -INFINITY;
       }
     }
     stage_wait();   // this thread's V chunks have landed
     __syncthreads();
     // ---- a warp per (head, token) row: maximum, weights (bf16: what is summed is what multiplies the values), sum, this tile's factor ----
-    for (int row = warp; row < H * PX_ROWS; row += 8) {
+    for (int row = warp; row < H * PX_ROWS; row += PX_WARPS) {
       const float s0 = Ss[(size_t)row * PX_SLD + lane];
       const float m_old = row_m[row];
       const float m_new = fmaxf(m_old, warp_max(s0));
@@ -1199,7 +1200,7 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
     // ---- O = O * factor + P V ----
 #pragma unroll
     for (int i = 0; i < NU; ++i) {
-      const int u = warp + 8 * i;
+      const int u = warp + PX_WARPS * i;
       if (u >= units) continue;
       const int h = u / VB, cb = u - h * VB;
 #pragma unroll
@@ -1218,7 +1219,7 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
   __syncthreads();   // every warp is done with the operand slabs: they become the output slab
 #pragma unroll
   for (int i = 0; i < NU; ++i) {
-    const int u = warp + 8 * i;
+    const int u = warp + PX_WARPS * i;
     if (u >= units) continue;
     const int h = u / VB, cb = u - h * VB;
     wmma::store_matrix_sync(Os + (size_t)h * PX_ROWS * L.OP + 16 * cb, oacc[i], L.OP, wmma::mem_row_major);
@@ -1229,7 +1230,7 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
     pair_cos_sin(pos_lo + r, m, V, g.rot_base, &cs[r * V + m], &cs[r * V + vhalf + m]);
   }
   __syncthreads();
-  for (int row = warp; row < H * PX_ROWS; row += 8) {
+  for (int row = warp; row < H * PX_ROWS; row += PX_WARPS) {
     const int h = row / PX_ROWS, r = row - h * PX_ROWS;
     if (r >= ntok) continue;
     const float inv = 1.0f / row_l[row];
@@ -1264,12 +1265,11 @@ int launch_premix_mma_h(int nu, const PremixMmaArgs& a, dim3 grid, size_t smem, 
   if (nu <= 1) return launch_premix_mma_t<HMAX, 1>(a, grid, smem, s);
   if (nu <= 2) return launch_premix_mma_t<HMAX, 2>(a, grid, smem, s);
   if (nu <= 4) return launch_premix_mma_t<HMAX, 4>(a, grid, smem, s);
-  if (nu <= 8) return launch_premix_mma_t<HMAX, 8>(a, grid, smem, s);
-  return launch_premix_mma_t<HMAX, 16>(a, grid, smem, s);
+  return launch_premix_mma_t<HMAX, 8>(a, grid, smem, s);   // (premix_mma_fits admits no more: sixteen fragments a thread would spill)
 }
 // whether the tensor-core form serves this geometry (else the plain kernel does)
 bool premix_mma_fits(const HeadsGeom& g) {
-  return g.dim % 16 == 0 && g.vdim % 16 == 0 && g.heads <= 32 && (g.heads * (g.vdim / 16) + 7) / 8 <= 16 && premix_mma_layout(g).total <= 224 * 1024;
+  return g.dim % 16 == 0 && g.vdim % 16 == 0 && g.heads <= 32 && (g.heads * (g.vdim / 16) + PX_WARPS - 1) / PX_WARPS <= 8 && premix_mma_layout(g).total <= 224 * 1024;
 }
 
 // ---- decode steps: one new token per sequence against a long cache ----
@@ -1522,7 +1522,7 @@ int launch_heads_attention_premix(const float* q, const void* k_cache, const voi
     PremixMmaArgs a{q, (const bf16*)k_cache, (const bf16*)v_cache, g, mix, block_table, bt_stride, block_size, tiles, (bf16*)out};
     const dim3 grid(ntiles, 64 / PX_ROWS);
     const size_t smem = premix_mma_layout(g).total;
-    const int nu = (g.heads * (g.vdim / 16) + 7) / 8;
+    const int nu = (g.heads * (g.vdim / 16) + PX_WARPS - 1) / PX_WARPS;
     if (g.heads <= 8) return launch_premix_mma_h<8>(nu, a, grid, smem, s);
     if (g.heads <= 16) return launch_premix_mma_h<16>(nu, a, grid, smem, s);
     return launch_premix_mma_h<32>(nu, a, grid, smem, s);

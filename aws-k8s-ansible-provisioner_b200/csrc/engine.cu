@@ -2901,8 +2901,11 @@ int mixed_engine_alloc(b2_engine* e) {
       max_act = std::max(max_act, (size_t)sp.top * sp.ff_dim);
     }
     if (sp.weights_of >= 0) {   // the layer runs with another layer's tensors: the same kinds and sizes, nothing of its own to hold
-      B2_REQUIRE(sp.weights_of < c.num_layers && sp.weights_of != l && e->specs[sp.weights_of].weights_of < 0, "layer %d: weights_of %d must name a layer with tensors of its own",
-                 l, sp.weights_of);
+      int root = sp.weights_of;   // a named layer may itself run with another's tensors: follow the chain to the layer that owns them
+      for (int hops = 0; root >= 0 && root < c.num_layers && e->specs[root].weights_of >= 0 && hops <= c.num_layers; ++hops) root = e->specs[root].weights_of;
+      B2_REQUIRE(root >= 0 && root < c.num_layers && root != l && e->specs[root].weights_of < 0, "layer %d: weights_of %d must lead to a layer with tensors of its own", l,
+                 sp.weights_of);
+      e->specs[l].weights_of = L.sp.weights_of = root;
       const b2_layer_spec& o = e->specs[sp.weights_of];
       B2_REQUIRE(o.mixer == sp.mixer && o.heads == sp.heads && o.kv_heads == sp.kv_heads && o.dim == sp.dim && o.vdim == sp.vdim && o.kv_rank == sp.kv_rank &&
                      o.q_rank == sp.q_rank && o.ff == sp.ff && o.ff_dim == sp.ff_dim && o.experts == sp.experts && o.top == sp.top,

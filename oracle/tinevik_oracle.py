@@ -174,7 +174,10 @@ def forward(cfg, w, tokens):
     x = w["embed"][tok] * float(cfg.get("embedding", {}).get("scale", 1.0))
     streams = []
     for i, L in enumerate(cfg["layers"]):
-        p = "l%d." % int(L.get("weights_of", i))
+        j = i
+        while cfg["layers"][j].get("weights_of") is not None:    # a named layer may itself name another: the tensors are the last one's
+            j = int(cfg["layers"][j]["weights_of"])
+        p = "l%d." % j
         ln = lambda name, y: layer_norm(y, w[p + name], w[p + name + ".b"], eps)
         x = x + ln("norm1b", MIXERS[L["type"]](ln("norm1", x), w, p + "mix.", L["mixer"], eps))
         mlp = L.get("mlp")

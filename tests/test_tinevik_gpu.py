@@ -173,6 +173,8 @@ SINGLE = {
     "more experts than a warp": [(gla(1, 8, 8, 2.0), moe(40, 2, 6))],
     "a layer run three times with one layer's tensors": [(att(2, 1, 8, 8, 0.4, rot=(100.0, 4, None)), dense(12)), (att(2, 1, 8, 8, 0.4, rot=(100.0, 4, None)), dense(12), 0),
                                                          (att(2, 1, 8, 8, 0.4, rot=(100.0, 4, None)), dense(12), 0)],
+    "tensors of a later layer, and of a layer that borrows its own": [(lat(2, 8, 6, 10, 7, 0.4, window=5), moe(4, 2, 6), 1), (lat(2, 8, 6, 10, 7, 0.4, window=5), moe(4, 2, 6)),
+                                                                      (lat(2, 8, 6, 10, 7, 0.4, window=5), moe(4, 2, 6), 0)],
 }
 
 
