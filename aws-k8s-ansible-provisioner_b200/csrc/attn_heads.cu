@@ -758,10 +758,11 @@ int launch_attention_t(const float* q, const void* k, const void* v, const Heads
 }
 
 // ---- mixers whose scores are mixed over the heads before the softmax ----
-// One CTA of 128 threads per token, a warp per head at a time (query heads, then key heads, then value heads).  The token's cosines and
+// One CTA per token (128 threads in long steps; 512 in short ones, where a token's heads should all be in flight at once), a warp per head
+// at a time (query heads, then key heads, then value heads).  The token's cosines and
 // sines are formed once: [rot_dims/2] for q and k (angles divided by rot_factor), [vdim/2] for the values.
 template <typename TC>
-__global__ void __launch_bounds__(128) heads_finish_halves_kernel(const float* __restrict__ proj, int ld, HeadsGeom g, const float* __restrict__ q_gain,
+__global__ void __launch_bounds__(512) heads_finish_halves_kernel(const float* __restrict__ proj, int ld, HeadsGeom g, const float* __restrict__ q_gain,
                                                                   const float* __restrict__ k_gain, const int32_t* __restrict__ positions,
                                                                   const int32_t* __restrict__ slots, float* __restrict__ q_out, TC* __restrict__ k_cache,
                                                                   TC* __restrict__ v_cache) {
@@ -770,21 +771,22 @@ __global__ void __launch_bounds__(128) heads_finish_halves_kernel(const float* _
   pdl_launch_dependents();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = positions[t], slot = slots[t];
+  const int nthr = blockDim.x, nwarp = nthr >> 5;
   const int half = g.rot_dims / 2, vhalf = g.rot_values ? g.vdim / 2 : 0;
   float* vcs = cs + 2 * half;
   const double inv_factor = g.rot_factor > 0.f ? 1.0 / (double)g.rot_factor : 1.0;
-  for (int i = threadIdx.x; i < half; i += 128) {
+  for (int i = threadIdx.x; i < half; i += nthr) {
     const double f = exp2(-2.0 * (double)i / (double)g.rot_dims * log2((double)g.rot_base)) * inv_factor;
     double sd, cd;
     sincos((double)pos * f, &sd, &cd);
     cs[i] = (float)cd;
     cs[half + i] = (float)sd;
   }
-  for (int i = threadIdx.x; i < vhalf; i += 128) pair_cos_sin(pos, i, g.vdim, g.rot_base, &vcs[i], &vcs[vhalf + i]);
+  for (int i = threadIdx.x; i < vhalf; i += nthr) pair_cos_sin(pos, i, g.vdim, g.rot_base, &vcs[i], &vcs[vhalf + i]);
   __syncthreads();
   const float* row = proj + (size_t)t * ld;
   const int nqk = g.heads + g.kv_heads;
-  for (int u = warp; u < nqk + g.kv_heads; u += 4) {
+  for (int u = warp; u < nqk + g.kv_heads; u += nwarp) {
     if (u < nqk) {
       const bool is_q = u < g.heads;
       const int a = is_q ? u : u - g.heads;
@@ -996,7 +998,7 @@ __global__ void __launch_bounds__(PM_WARPS * 32) heads_attention_premix_kernel(P
 // ---- the same pass on warp-level tensor-core MMAs (bf16 caches, prompt portions, head sizes in multiples of 16) ----
 // One CTA of sixteen warps per 16 query tokens and ALL heads; keys go by in tiles of 32.  Per tile: the K rows of every key/value head are
 // staged (bf16) and every query head forms S = Q K^T, one 16 x 16 block per warp at a time, into an fp32 slab [heads][16][32]; the V rows
-// take the K rows' place while every thread takes one (token, key) pair, reads the pair's scores of every head into registers (scale, cap),
+// take the K rows' place while every thread takes one (token, key) pair, reads the pair's scores head by head (scale, cap),
 // mixes them (two heads per packed fp32 multiply-add, each head's sum in the order of the heads) and writes them back masked; then two
 // threads per (token, head) row update the row's maximum and sum and write the weights as bf16; then the warps accumulate P V into the
 // output fragments they own (unit u = head * (vdim / 16) + column block belongs to warp u mod 16), rescaled once per tile by the rows' factors.  The end goes through shared memory: division, the turn back by the query's
@@ -1103,11 +1105,27 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
   for (int u = 0; u < NU; ++u) wmma::fill_fragment(oacc[u], 0.f);
   const int units = H * VB;
   const int32_t* bt = a.block_table + (size_t)tl.bt_row * a.bt_stride;
-  auto stage_rows = [&](const bf16* cache, int width) {   // the tile's rows of every key/value head, zeros past the last key
-    const int cpr = width / 8, per_key = G * cpr;   // 16-byte chunks per head row; a key's cache row holds the heads side by side
+  // a chunk index splits into (key, head, chunk of the head row) by multiplications: q = n / d as the high word of n * ceil(2^32 / d), exact
+  // for n < 2^16 and 2 <= d < 2^16 (32 keys of at most a few hundred chunks each)
+  struct StageGeom {
+    int cpr, per_key;          // 16-byte chunks per head row; per key (a key's cache row holds the heads side by side)
+    unsigned m_cpr, m_key;
+  };
+  auto stage_geom = [&](int width) {
+    StageGeom sg;
+    sg.cpr = width / 8;
+    sg.per_key = G * sg.cpr;
+    sg.m_cpr = (unsigned)((0x100000000ull + sg.cpr - 1) / sg.cpr);
+    sg.m_key = (unsigned)((0x100000000ull + sg.per_key - 1) / sg.per_key);
+    return sg;
+  };
+  const StageGeom sg_k = stage_geom(D), sg_v = stage_geom(V);
+  auto stage_rows = [&](const bf16* cache, int width, const StageGeom& sg) {   // the tile's rows of every key/value head, zeros past the last key
+    const int total = PX_KEYS * sg.per_key;
 #pragma unroll 4
-    for (int idx = tid; idx < PX_KEYS * per_key; idx += PX_THREADS) {
-      const int j = idx / per_key, rest = idx - j * per_key, kvh = rest / cpr, c = rest - kvh * cpr;
+    for (int idx = tid; idx < total; idx += PX_THREADS) {
+      const int j = (int)__umulhi((unsigned)idx, sg.m_key), rest = idx - j * sg.per_key;
+      const int kvh = (int)__umulhi((unsigned)rest, sg.m_cpr), c = rest - kvh * sg.cpr;
       const int kr = key_row[j];
       // asynchronous 16-byte copies (zero-filled past the last key): every chunk of a thread is in flight at once
       const bf16* src = cache + (size_t)(kr >= 0 ? kr : 0) * G * width + (size_t)rest * 8;
@@ -1124,7 +1142,7 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
       key_row[tid] = kp <= pos_hi ? bt[kp / a.block_size] * a.block_size + kp % a.block_size : -1;
     }
     __syncthreads();
-    stage_rows(a.k_cache, D);
+    stage_rows(a.k_cache, D, sg_k);
     stage_wait();
     __syncthreads();
     // ---- S = Q K^T: unit u = head * 2 + key block ----
@@ -1143,7 +1161,7 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
       wmma::store_matrix_sync(Ss + (size_t)h * PX_ROWS * PX_SLD + 16 * kb, acc, PX_SLD, wmma::mem_row_major);
     }
     __syncthreads();
-    stage_rows(a.v_cache, V);   // (the K rows are consumed; the loads fly while the scores are mixed)
+    stage_rows(a.v_cache, V, sg_v);   // (the K rows are consumed; the loads fly while the scores are mixed)
     // ---- scale, cap, mix over the heads, mask: a thread takes ONE (token, key) pair.  It walks the heads b in their order, reads the pair's
     //      score of head b (scale, cap) and adds its share to the mixed score of every head h, two heads per packed fp32 multiply-add with
     //      the matrix column b read four entries a load; every sum therefore runs over b upwards, as the plain kernel's does ----
@@ -1153,11 +1171,12 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
 #pragma unroll
       for (int h2 = 0; h2 < HMAX / 2; ++h2) mixed[h2] = 0ull;
       const float* scol = Ss + (size_t)r0 * PX_SLD + j;
+      const float two_over_cap = g.softcap > 0.f ? 2.0f / g.softcap : 0.f;
 #pragma unroll 4
       for (int b = 0; b < H; ++b) {
         float v = scol[(size_t)b * PX_ROWS * PX_SLD] * g.scale;
         // cap * tanh(v / cap) as cap * (1 - 2 / (exp(2 v / cap) + 1)): the operands of this kernel are bf16, its fast exponential is not what bounds it
-        if (g.softcap > 0.f) v = g.softcap * (1.0f - __fdividef(2.0f, __expf(2.0f * v / g.softcap) + 1.0f));
+        if (g.softcap > 0.f) v = g.softcap * (1.0f - __fdividef(2.0f, __expf(v * two_over_cap) + 1.0f));
         unsigned long long vv;
         asm("mov.b64 %0, {%1, %1};" : "=l"(vv) : "f"(v));
         const float* tcol = Tk + b * HMAX;   // (padded to HMAX entries, zeros behind the heads)
@@ -1181,15 +1200,38 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
     }
     stage_wait();   // this thread's V chunks have landed
     __syncthreads();
-    // ---- a warp per (head, token) row: maximum, weights (bf16: what is summed is what multiplies the values), sum, this tile's factor ----
-    for (int row = warp; row < H * PX_ROWS; row += PX_WARPS) {
-      const float s0 = Ss[(size_t)row * PX_SLD + lane];
+    // ---- two threads per (head, token) row, sixteen keys each: maximum, weights (bf16: what is summed is what multiplies the values), sum,
+    //      this tile's factor ----
+    for (int idx = tid; idx < 2 * H * PX_ROWS; idx += PX_THREADS) {
+      const int row = idx >> 1, part = idx & 1;
+      float sv[16];
+      const float4* s4 = reinterpret_cast<const float4*>(Ss + (size_t)row * PX_SLD + 16 * part);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 x = s4[i];
+        sv[4 * i] = x.x; sv[4 * i + 1] = x.y; sv[4 * i + 2] = x.z; sv[4 * i + 3] = x.w;
+      }
+      float mx = sv[0];
+#pragma unroll
+      for (int i = 1; i < 16; ++i) mx = fmaxf(mx, sv[i]);
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       const float m_old = row_m[row];
-      const float m_new = fmaxf(m_old, warp_max(s0));
-      const bf16 p0 = __float2bfloat16_rn(s0 == -INFINITY ? 0.f : expf(s0 - m_new));
-      Ps[(size_t)row * PX_PLD + lane] = p0;
-      const float psum = warp_sum(__bfloat162float(p0));
-      if (lane == 0) {
+      const float m_new = fmaxf(m_old, mx);
+      float psum = 0.f;
+      unsigned pk[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float e0 = sv[2 * i] == -INFINITY ? 0.f : expf(sv[2 * i] - m_new), e1 = sv[2 * i + 1] == -INFINITY ? 0.f : expf(sv[2 * i + 1] - m_new);
+        const __nv_bfloat162 pp = __floats2bfloat162_rn(e0, e1);
+        pk[i] = *reinterpret_cast<const unsigned*>(&pp);
+        psum += __low2float(pp) + __high2float(pp);
+      }
+      uint4* pd = reinterpret_cast<uint4*>(Ps + (size_t)row * PX_PLD + 16 * part);
+      pd[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      pd[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+      psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+      __syncwarp();   // (both threads of a row have read its old maximum)
+      if (part == 0) {
         const float corr = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
         row_m[row] = m_new;
         row_l[row] = row_l[row] * corr + psum;
@@ -1401,24 +1443,25 @@ __global__ void __launch_bounds__(1024) heads_attention_premix_decode_kernel(Pre
 }
 
 // folds the splits of every (row, head) in split order, divides, turns the sum back by the row's position, rounds; a CTA per row, a warp
-// per head at a time (lane s holds split s: at most 32 splits); the row's cosines and sines are formed once for all heads
+// per head at a time (lane s holds split s: at most 32 splits; the CTA has as many warps as heads, up to sixteen, so that every head's
+// partial sums are in flight at once, eight splits a batch); the row's cosines and sines are formed once for all heads
 template <typename TX>
-__global__ void __launch_bounds__(128) premix_merge_kernel(const float* __restrict__ partial, int nsplit, HeadsGeom g, const int32_t* __restrict__ positions,
+__global__ void __launch_bounds__(512) premix_merge_kernel(const float* __restrict__ partial, int nsplit, HeadsGeom g, const int32_t* __restrict__ positions,
                                                            const int32_t* __restrict__ seq_lens, TX* __restrict__ out) {
-  extern __shared__ float sm[];   // [4 warps][vdim], then cos [vdim/2] | sin [vdim/2]
+  extern __shared__ float sm[];   // [warps][vdim], then cos [vdim/2] | sin [vdim/2]
   pdl_wait();
   pdl_launch_dependents();
-  const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nthr = blockDim.x, nwarp = nthr >> 5;
   const int H = g.heads, V = g.vdim, vhalf = g.rot_values ? V / 2 : 0;
   const bool empty = seq_lens[b] <= 0;
   float* row = sm + warp * V;
-  float* cs = sm + 4 * V;
+  float* cs = sm + nwarp * V;
   if (!empty) {
     const int pos = positions[b];
-    for (int i = threadIdx.x; i < vhalf; i += 128) pair_cos_sin(pos, i, V, g.rot_base, &cs[i], &cs[vhalf + i]);
+    for (int i = threadIdx.x; i < vhalf; i += nthr) pair_cos_sin(pos, i, V, g.rot_base, &cs[i], &cs[vhalf + i]);
   }
   __syncthreads();
-  for (int h = warp; h < H; h += 4) {
+  for (int h = warp; h < H; h += nwarp) {
     TX* dst = out + ((size_t)b * H + h) * V;
     if (empty) {
       for (int d = lane; d < V; d += 32) stf(dst + d, 0.f);
@@ -1434,9 +1477,17 @@ __global__ void __launch_bounds__(128) premix_merge_kernel(const float* __restri
     for (int d0 = 0; d0 < V; d0 += 32) {
       const int d = d0 + lane;
       float acc = 0.f;
-      for (int s2 = 0; s2 < nsplit; ++s2) {
-        const float w2 = __shfl_sync(0xffffffffu, wgt, s2);
-        if (d < V && w2 != 0.f) acc = fmaf(p[s2 * stride + 2 + d], w2, acc);
+      for (int s2 = 0; s2 < nsplit; s2 += 8) {
+        float w2[8], x[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {   // (a split without keys left its sums unwritten: weight 0 reads nothing)
+          const float w = __shfl_sync(0xffffffffu, wgt, (s2 + k) & 31);
+          w2[k] = s2 + k < nsplit ? w : 0.f;
+          x[k] = d < V && w2[k] != 0.f ? p[(s2 + k) * stride + 2 + d] : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (w2[k] != 0.f) acc = fmaf(x[k], w2[k], acc);
       }
       if (d < V) row[d] = acc * inv;
     }
@@ -1501,11 +1552,12 @@ int launch_heads_finish_halves(const float* proj, int ld, const HeadsGeom& g, co
   B2_REQUIRE(g.rot_dims >= 0 && g.rot_dims <= g.dim && g.rot_dims % 2 == 0, "heads_finish_halves: rot dims %d must be even and <= dim %d", g.rot_dims, g.dim);
   B2_REQUIRE(!g.rot_values || g.vdim % 2 == 0, "heads_finish_halves: rotated values need an even vdim (%d)", g.vdim);
   const size_t smem = (size_t)(g.rot_dims + (g.rot_values ? g.vdim : 0) + 2) * sizeof(float);
+  const dim3 block(T <= 4 * 148 ? 512 : 128);   // few tokens: every head of a token gets a warp of its own
   if (cache_f32)
-    B2_CUDA_OK(b2_launch(heads_finish_halves_kernel<float>, dim3(T), dim3(128), smem, s, proj, ld, g, q_gain, k_gain, positions, slots, q_out,
+    B2_CUDA_OK(b2_launch(heads_finish_halves_kernel<float>, dim3(T), block, smem, s, proj, ld, g, q_gain, k_gain, positions, slots, q_out,
                          (float*)k_cache, (float*)v_cache));
   else
-    B2_CUDA_OK(b2_launch(heads_finish_halves_kernel<bf16>, dim3(T), dim3(128), smem, s, proj, ld, g, q_gain, k_gain, positions, slots, q_out,
+    B2_CUDA_OK(b2_launch(heads_finish_halves_kernel<bf16>, dim3(T), block, smem, s, proj, ld, g, q_gain, k_gain, positions, slots, q_out,
                          (bf16*)k_cache, (bf16*)v_cache));
   return 0;
 }
@@ -1535,9 +1587,10 @@ int launch_heads_attention_premix(const float* q, const void* k_cache, const voi
       PremixDecodeArgs a{q, k_cache, v_cache, g, mix, block_table, bt_stride, block_size, positions, seq_lens, scratch, ns};
       if (cache_f32) B2_TRY_RC(launch_premix_decode_t<float>(a, T, smem, s));
       else B2_TRY_RC(launch_premix_decode_t<bf16>(a, T, smem, s));
-      const size_t msm = (size_t)5 * g.vdim * sizeof(float);
-      if (out_f32) B2_CUDA_OK(b2_launch(premix_merge_kernel<float>, dim3(T), dim3(128), msm, s, (const float*)scratch, ns, g, positions, seq_lens, (float*)out));
-      else B2_CUDA_OK(b2_launch(premix_merge_kernel<bf16>, dim3(T), dim3(128), msm, s, (const float*)scratch, ns, g, positions, seq_lens, (bf16*)out));
+      const int mw = std::min(16, std::max(4, g.heads));   // warps of a merge CTA
+      const size_t msm = (size_t)(mw + 1) * g.vdim * sizeof(float);
+      if (out_f32) B2_CUDA_OK(b2_launch(premix_merge_kernel<float>, dim3(T), dim3(32 * mw), msm, s, (const float*)scratch, ns, g, positions, seq_lens, (float*)out));
+      else B2_CUDA_OK(b2_launch(premix_merge_kernel<bf16>, dim3(T), dim3(32 * mw), msm, s, (const float*)scratch, ns, g, positions, seq_lens, (bf16*)out));
       return 0;
     }
   }
