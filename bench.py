@@ -469,7 +469,7 @@ BUMALIX_SIZES = {"w1024": (1024, 8, 3072), "w2048": (2048, 16, 6144), "w4096": (
 
 def bumalix_model_cfg(width, heads, inter, layers=4, vocab=32000):
     par = {"left": {"heads": heads, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 512}},
-           "right": {"heads": heads // 2, "dim": 128, "vdim": 256, "tau": 16.0}}
+           "right": {"heads": heads // 2, "dim": 128, "vdim": 256, "tau": 8.0}}
     dlt = {"heads": heads, "kv_heads": heads, "dim": 128, "vdim": 128, "conv": 4}
     dense = {"kind": "dense", "ff": min((3 * inter // 2 + 255) // 256 * 256, 16384)}   # two matrices with the parameters of Qwen3's three (a decode step's
                                                                                        # weight-streaming products stage rows of at most 16384 numbers)
@@ -480,14 +480,14 @@ def bumalix_model_cfg(width, heads, inter, layers=4, vocab=32000):
 
 
 # ---- --family tinevik: width, heads (128 wide, two per kv head), Qwen3's feed-forward width.  Four layers: gated linear attention (half as many heads,
-#      128 x 256), head-mixed softmax attention with rotated values (64 of 128 entries rotated, angles halved, cap 30), windowed latent attention (latent
+#      128 x 256), head-mixed softmax attention with rotated values (64 of 128 entries rotated, angles quartered, cap 50), windowed latent attention (latent
 #      512, query latent width / 2, window 512), and the first layer's tensors once more; an xIELU feed-forward with Qwen3's parameter count in two
 #      matrices behind the state mixers, 16 table-routed clamped experts (two per token, Qwen3's active count) behind the others; vocab 32000.  The closest
 #      existing family is Bumalix (matrix states beside softmax attention, routed experts, an fp32 stream), which runs beside it at the same sizes.
 def tinevik_model_cfg(width, heads, inter, vocab=32000):
-    gla = {"heads": heads // 2, "dim": 128, "vdim": 256, "tau": 16.0}
-    att = {"heads": heads, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
-           "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 2.0}}}
+    gla = {"heads": heads // 2, "dim": 128, "vdim": 256, "tau": 8.0}
+    att = {"heads": heads, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0,
+           "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0}}}
     lat = {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": 512, "q_rank": width // 2, "scale": 128 ** -0.5, "mask": {"size": 512}}
     dense = {"kind": "dense", "ff": min((3 * inter // 2 + 255) // 256 * 256, 16384)}
     moe = {"kind": "moe", "expert": {"ff": (inter // 2 + 63) // 64 * 64, "limit": 7.0}, "router": {"experts": 16, "top": 2}}
