@@ -205,6 +205,35 @@ def test_bf16_close_to_the_restatement(make):
             assert err(e.get_logits(1)[0], ref[p]) < 3 * BF16_BAR, "decoded position %d" % p
 
 
+@pytest.mark.parametrize("heads,kv,dim,vdim", [(12, 4, 48, 64), (20, 20, 16, 32), (16, 8, 64, 128), (3, 1, 32, 16)])
+def test_bf16_head_mixed_attention_on_tensor_cores(heads, kv, dim, vdim):
+    """bf16 prompt portions of head sizes in multiples of 16 take the tensor-core form of the head-mixed attention, decode steps the form that
+    splits the keys: several head counts (above and below a register tile of heads, one key/value head, as many as heads), with sharpened scores,
+    whole prompts against portions that start and end inside key tiles, and decoding behind them.  A mixing matrix applied the wrong way round,
+    a key tile that is lost or a value turned by the wrong position moves the logits far beyond bf16 rounding."""
+    cfg = model([(att(heads, kv, dim, vdim, dim ** -0.5, rot=(3000.0, dim // 2, 2.0), cap=25.0), dense(64)),
+                 (att(heads, kv, dim, vdim, dim ** -0.5, rot=(3000.0, dim // 2, 2.0), cap=25.0), dense(64), 0)], vocab=211, width=96)
+    w = sharpen(cfg, random_weights(cfg, seed=23), factor=3.0)
+    toks = tokens(cfg, 230, 24)
+    ref = ref_logits(cfg, w, toks)
+    swapped = dict(w)
+    swapped["l0.mix.talk"] = w["l0.mix.talk"].t().contiguous()
+    assert err(ref_logits(cfg, swapped, toks)[100:], ref[100:]) > 3 * BF16_BAR     # the test would see the matrix transposed
+    with engine(cfg, w, f32=False) as e:
+        for cuts, decode_from in ([230], 230), ([70, 33, 2, 47, 17, 40], 209):
+            sid = e.seq_create(len(toks))
+            at, rel = 0, []
+            for c in cuts:
+                lg, _ = e.prefill_logits([sid], [toks[at:at + c]], list(range(c)))
+                rel += list(np.abs(lg - ref[at:at + c]).max(axis=1) / np.abs(ref).max())
+                at += c
+            for p_ in range(at, len(toks)):
+                e.decode_step([sid], in_tokens=[toks[p_]], want_output=False)
+                rel.append(np.abs(e.get_logits(1)[0] - ref[p_]).max() / np.abs(ref).max())
+            e.seq_free(sid)
+            assert at == decode_from and np.median(rel) < BF16_BAR / 3 and max(rel) < 3 * BF16_BAR, (cuts, np.median(rel), max(rel))
+
+
 def test_bf16_long_step_runs_the_experts_one_by_one():
     """A step with at least 2048 (token, choice) pairs takes the per-expert tensor-core products; short portions of the same prompt take
     the ragged ones: both agree with the restatement."""
