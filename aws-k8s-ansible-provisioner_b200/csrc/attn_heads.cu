@@ -1041,7 +1041,6 @@ __host__ __device__ inline PremixMmaLayout premix_mma_layout(const HeadsGeom& g)
 // HMAX: register slots for one pair's scores (heads <= HMAX); NU: output fragments per warp (heads * vdim / 16 <= PX_WARPS * NU)
 template <int HMAX, int NU>
 __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kernel(PremixMmaArgs a) {
-  using namespace nvcuda;
   extern __shared__ __align__(128) unsigned char smraw[];
   pdl_wait();
   pdl_launch_dependents();
@@ -1087,22 +1086,14 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
     Tk[i] = h >= H ? 0.f : a.mix != nullptr ? a.mix[h * H + b] : (h == b ? 1.f : 0.f);
   }
   if (tid < PX_ROWS) row_pos[tid] = tid < ntok ? pos_lo + tid : -1;
-  // ---- which row of its 16 x 16 tile each accumulator element of this thread belongs to (the layout of a fragment is the compiler's
-  //      business): read back from a tile that holds its own row numbers ----
-  using OFrag = wmma::fragment<wmma::accumulator, 16, 16, 16, float>;
-  constexpr int NE = OFrag::num_elements;
-  OFrag oacc[NU];
-  int frag_row[NE];
-  {
-    __syncthreads();
-    if (tid < 256) Ss[tid] = (float)(tid >> 4);   // a 16 x 16 tile, row-major
-    __syncthreads();
-    wmma::load_matrix_sync(oacc[0], Ss, 16, wmma::mem_row_major);
+  // ---- output accumulators: unit u = head * (vdim / 16) + column block holds a 16 x 16 block as two m16n8 accumulators (element 0, 1: row
+  //      lane / 4, columns 2 (lane % 4) and the next; element 2, 3: row lane / 4 + 8) ----
+  float oacc[NU][2][4];
 #pragma unroll
-    for (int e = 0; e < NE; ++e) frag_row[e] = (int)oacc[0].x[e];
-  }
+  for (int u = 0; u < NU; ++u)
 #pragma unroll
-  for (int u = 0; u < NU; ++u) wmma::fill_fragment(oacc[u], 0.f);
+    for (int e = 0; e < 4; ++e) oacc[u][0][e] = oacc[u][1][e] = 0.f;
+  const int fg = lane >> 2, ft = lane & 3;
   const int units = H * VB;
   const int32_t* bt = a.block_table + (size_t)tl.bt_row * a.bt_stride;
   // a chunk index splits into (key, head, chunk of the head row) by multiplications: q = n / d as the high word of n * ceil(2^32 / d), exact
@@ -1145,20 +1136,27 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
     stage_rows(a.k_cache, D, sg_k);
     stage_wait();
     __syncthreads();
-    // ---- S = Q K^T: unit u = head * 2 + key block ----
+    // ---- S = Q K^T: unit u = head * 2 + key block; per 16 entries of the heads one ldmatrix for the queries' 16 x 16 block, one for the
+    //      two 8-key groups' blocks, two MMAs ----
     for (int u = warp; u < H * 2; u += PX_WARPS) {
       const int h = u >> 1, kb = u & 1;
-      wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
-      wmma::fill_fragment(acc, 0.f);
-      const bf16* kbase = Ks + ((size_t)(h / rep) * PX_KEYS + 16 * kb) * L.KP;
+      float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      const uint32_t qaddr = smem_u32(Qs + ((size_t)h * PX_ROWS + (lane & 15)) * L.QP + (lane >> 4) * 8);
+      const uint32_t kaddr = smem_u32(Ks + ((size_t)(h / rep) * PX_KEYS + 16 * kb + (lane & 7) + ((lane >> 4) & 1) * 8) * L.KP + ((lane >> 3) & 1) * 8);
+#pragma unroll 4
       for (int d = 0; d < D; d += 16) {
-        wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fq;
-        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> fk;
-        wmma::load_matrix_sync(fq, Qs + (size_t)h * PX_ROWS * L.QP + d, L.QP);
-        wmma::load_matrix_sync(fk, kbase + d, L.KP);
-        wmma::mma_sync(acc, fq, fk, acc);
+        uint32_t qa[4], kf[4];
+        ldmatrix_x4(qa, qaddr + d * 2);
+        ldmatrix_x4(kf, kaddr + d * 2);
+        mma_bf16_16816(acc[0], qa, kf[0], kf[1]);
+        mma_bf16_16816(acc[1], qa, kf[2], kf[3]);
       }
-      wmma::store_matrix_sync(Ss + (size_t)h * PX_ROWS * PX_SLD + 16 * kb, acc, PX_SLD, wmma::mem_row_major);
+      float* srow = Ss + ((size_t)h * PX_ROWS + fg) * PX_SLD + 16 * kb + 2 * ft;
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        *reinterpret_cast<float2*>(srow + 8 * n) = make_float2(acc[n][0], acc[n][1]);
+        *reinterpret_cast<float2*>(srow + 8 * PX_SLD + 8 * n) = make_float2(acc[n][2], acc[n][3]);
+      }
     }
     __syncthreads();
     stage_rows(a.v_cache, V, sg_v);   // (the K rows are consumed; the loads fly while the scores are mixed)
@@ -1239,22 +1237,27 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
       }
     }
     __syncthreads();   // weights, factors and the V rows are in place
-    // ---- O = O * factor + P V ----
+    // ---- O = O * factor + P V: per 16 keys one ldmatrix for the weights' block, one (transposing) for the values' two 8-column groups ----
 #pragma unroll
     for (int i = 0; i < NU; ++i) {
       const int u = warp + PX_WARPS * i;
       if (u >= units) continue;
       const int h = u / VB, cb = u - h * VB;
+      const float f0 = row_f[h * PX_ROWS + fg], f1 = row_f[h * PX_ROWS + fg + 8];
 #pragma unroll
-      for (int e = 0; e < NE; ++e) oacc[i].x[e] *= row_f[h * PX_ROWS + frag_row[e]];
-      const bf16* vbase = Ks + (size_t)(h / rep) * PX_KEYS * L.KP + 16 * cb;
+      for (int n = 0; n < 2; ++n) {
+        oacc[i][n][0] *= f0; oacc[i][n][1] *= f0;
+        oacc[i][n][2] *= f1; oacc[i][n][3] *= f1;
+      }
+      const uint32_t paddr = smem_u32(Ps + ((size_t)h * PX_ROWS + (lane & 15)) * PX_PLD + (lane >> 4) * 8);
+      const uint32_t vaddr = smem_u32(Ks + ((size_t)(h / rep) * PX_KEYS + (lane & 7) + ((lane >> 3) & 1) * 8) * L.KP + 16 * cb + (lane >> 4) * 8);
 #pragma unroll
       for (int kk = 0; kk < PX_KEYS; kk += 16) {
-        wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fp;
-        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> fv;
-        wmma::load_matrix_sync(fp, Ps + (size_t)h * PX_ROWS * PX_PLD + kk, PX_PLD);
-        wmma::load_matrix_sync(fv, vbase + (size_t)kk * L.KP, L.KP);
-        wmma::mma_sync(oacc[i], fp, fv, oacc[i]);
+        uint32_t pa[4], vb[4];
+        ldmatrix_x4(pa, paddr + kk * 2);
+        ldmatrix_x4_trans(vb, vaddr + (uint32_t)(kk * L.KP) * 2);
+        mma_bf16_16816(oacc[i][0], pa, vb[0], vb[1]);
+        mma_bf16_16816(oacc[i][1], pa, vb[2], vb[3]);
       }
     }
   }
@@ -1264,7 +1267,12 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
     const int u = warp + PX_WARPS * i;
     if (u >= units) continue;
     const int h = u / VB, cb = u - h * VB;
-    wmma::store_matrix_sync(Os + (size_t)h * PX_ROWS * L.OP + 16 * cb, oacc[i], L.OP, wmma::mem_row_major);
+    float* orow = Os + ((size_t)h * PX_ROWS + fg) * L.OP + 16 * cb + 2 * ft;
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      *reinterpret_cast<float2*>(orow + 8 * n) = make_float2(oacc[i][n][0], oacc[i][n][1]);
+      *reinterpret_cast<float2*>(orow + (size_t)8 * L.OP + 8 * n) = make_float2(oacc[i][n][2], oacc[i][n][3]);
+    }
   }
   const int vhalf = g.rot_values ? V / 2 : 0;
   for (int i = tid; i < ntok * vhalf; i += PX_THREADS) {
