@@ -1061,8 +1061,10 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
   int* key_row = row_pos + PX_ROWS;                         // [32]
   float* cs = reinterpret_cast<float*>(smraw + L.cs_off);
 
-  const PrefillTile tl = a.tiles[blockIdx.x];
-  const int tok0 = blockIdx.y * PX_ROWS;
+  // CTAs start in the order of their index: the list of tiles and the blocks of a tile are walked backwards, so that the late positions of a
+  // prompt (the most key tiles) start first and the last CTAs to start are short ones
+  const PrefillTile tl = a.tiles[gridDim.x - 1 - blockIdx.x];
+  const int tok0 = (gridDim.y - 1 - blockIdx.y) * PX_ROWS;
   const int ntok = min(PX_ROWS, tl.nrows - tok0);
   if (ntok <= 0) return;
   const int q_row0 = tl.q_row0 + tok0, pos_lo = tl.q_pos0 + tok0, pos_hi = pos_lo + ntok - 1;
@@ -1169,12 +1171,19 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
 #pragma unroll
       for (int h2 = 0; h2 < HMAX / 2; ++h2) mixed[h2] = 0ull;
       const float* scol = Ss + (size_t)r0 * PX_SLD + j;
-      const float two_over_cap = g.softcap > 0.f ? 2.0f / g.softcap : 0.f;
+      const float exp_scale = g.softcap > 0.f ? g.scale * 2.0f * 1.4426950408889634f / g.softcap : 0.f, minus_two_cap = -2.0f * g.softcap;
 #pragma unroll 4
       for (int b = 0; b < H; ++b) {
-        float v = scol[(size_t)b * PX_ROWS * PX_SLD] * g.scale;
-        // cap * tanh(v / cap) as cap * (1 - 2 / (exp(2 v / cap) + 1)): the operands of this kernel are bf16, its fast exponential is not what bounds it
-        if (g.softcap > 0.f) v = g.softcap * (1.0f - __fdividef(2.0f, __expf(v * two_over_cap) + 1.0f));
+        float v = scol[(size_t)b * PX_ROWS * PX_SLD];
+        // cap * tanh(s / cap) with s = v * scale as cap - 2 cap / (2^(s * 2 log2(e) / cap) + 1): the operands of this kernel are bf16, its fast
+        // exponential and reciprocal are not what bounds it
+        if (g.softcap > 0.f) {
+          float ex;
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(v * exp_scale));
+          v = g.softcap + __fdividef(minus_two_cap, ex + 1.0f);
+        } else {
+          v *= g.scale;
+        }
         unsigned long long vv;
         asm("mov.b64 %0, {%1, %1};" : "=l"(vv) : "f"(v));
         const float* tcol = Tk + b * HMAX;   // (padded to HMAX entries, zeros behind the heads)
@@ -1219,7 +1228,12 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
       unsigned pk[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float e0 = sv[2 * i] == -INFINITY ? 0.f : expf(sv[2 * i] - m_new), e1 = sv[2 * i + 1] == -INFINITY ? 0.f : expf(sv[2 * i + 1] - m_new);
+        // (the weights are rounded to bf16 next: the approximate exponential loses nothing)
+        float e0, e1;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"((sv[2 * i] - m_new) * 1.4426950408889634f));
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"((sv[2 * i + 1] - m_new) * 1.4426950408889634f));
+        if (sv[2 * i] == -INFINITY) e0 = 0.f;
+        if (sv[2 * i + 1] == -INFINITY) e1 = 0.f;
         const __nv_bfloat162 pp = __floats2bfloat162_rn(e0, e1);
         pk[i] = *reinterpret_cast<const unsigned*>(&pp);
         psum += __low2float(pp) + __high2float(pp);
