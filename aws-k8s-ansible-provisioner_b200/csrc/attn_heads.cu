@@ -1032,8 +1032,8 @@ __host__ __device__ inline PremixMmaLayout premix_mma_layout(const HeadsGeom& g)
   const size_t main_end = L.p_off + (size_t)H * PX_ROWS * PX_PLD * 2;
   const size_t out_end = (size_t)H * PX_ROWS * L.OP * 4;              // the output slab reuses everything from the start
   L.misc_off = ((main_end > out_end ? main_end : out_end) + 127) / 128 * 128;
-  // misc: running maximum, sum, this tile's factor [heads * 16] each, the mixing matrix [heads][up to 32], positions [16], cache rows [32]
-  L.cs_off = L.misc_off + ((size_t)3 * H * PX_ROWS + (size_t)H * 32 + PX_ROWS + PX_KEYS) * 4;
+  // misc: running maximum, sum, this tile's factor [heads * 16] each, the mixing matrix [heads][up to 32], positions [16], cache rows [2][32]
+  L.cs_off = L.misc_off + ((size_t)3 * H * PX_ROWS + (size_t)H * 32 + PX_ROWS + 2 * PX_KEYS) * 4;
   L.total = L.cs_off + (size_t)PX_ROWS * V * 4;                        // cos [16][V/2] | sin [16][V/2]
   return L;
 }
@@ -1058,7 +1058,7 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
   float* row_f = row_l + H * PX_ROWS;
   float* Tk = row_f + H * PX_ROWS;                          // [H][HMAX], transposed: entry [b][h] weighs head b's score in head h's mix
   int* row_pos = reinterpret_cast<int*>(Tk + H * HMAX);     // [16]
-  int* key_row = row_pos + PX_ROWS;                         // [32]
+  int* key_row = row_pos + PX_ROWS;                         // [2][32]: this tile's cache rows and the next tile's
   float* cs = reinterpret_cast<float*>(smraw + L.cs_off);
 
   // CTAs start in the order of their index: the list of tiles and the blocks of a tile are walked backwards, so that the late positions of a
@@ -1113,7 +1113,7 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
     return sg;
   };
   const StageGeom sg_k = stage_geom(D), sg_v = stage_geom(V);
-  auto stage_rows = [&](const bf16* cache, int width, const StageGeom& sg) {   // the tile's rows of every key/value head, zeros past the last key
+  auto stage_rows = [&](const bf16* cache, int width, const StageGeom& sg, const int* key_row) {   // the tile's rows of every key/value head, zeros past the last key
     const int total = PX_KEYS * sg.per_key;
 #pragma unroll 4
     for (int idx = tid; idx < total; idx += PX_THREADS) {
@@ -1128,14 +1128,16 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
   };
   auto stage_wait = [&]() { asm volatile("cp.async.wait_group 0;" ::: "memory"); };
   const int k_first = g.window > 0 ? max(0, pos_lo - g.window + 1) / PX_KEYS * PX_KEYS : 0;
-  for (int k0 = k_first; k0 <= pos_hi; k0 += PX_KEYS) {
-    __syncthreads();   // the tile before is consumed
-    if (tid < PX_KEYS) {
-      const int kp = k0 + tid;
-      key_row[tid] = kp <= pos_hi ? bt[kp / a.block_size] * a.block_size + kp % a.block_size : -1;
-    }
-    __syncthreads();
-    stage_rows(a.k_cache, D, sg_k);
+  // the cache rows of a tile's keys are looked up a tile ahead (thirty-two threads, beside the mix), so that no tile waits for its block table
+  auto cache_row = [&](int kp) { return kp <= pos_hi ? bt[kp / a.block_size] * a.block_size + kp % a.block_size : -1; };
+  if (tid < PX_KEYS) key_row[tid] = cache_row(k_first + tid);
+  int cur = 0;
+  for (int k0 = k_first; k0 <= pos_hi; k0 += PX_KEYS, cur ^= 1) {
+    const int* rows_now = key_row + cur * PX_KEYS;
+    int row_ahead = -1;   // (read here, stored behind the mix: its latency hides behind this tile's work)
+    if (tid < PX_KEYS && k0 + PX_KEYS <= pos_hi) row_ahead = cache_row(k0 + PX_KEYS + tid);
+    __syncthreads();   // the tile before is consumed; this tile's cache rows are in place
+    stage_rows(a.k_cache, D, sg_k, rows_now);
     stage_wait();
     __syncthreads();
     // ---- S = Q K^T: unit u = head * 2 + key block; per 16 entries of the heads one ldmatrix for the queries' 16 x 16 block, one for the
@@ -1161,7 +1163,8 @@ __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kern
       }
     }
     __syncthreads();
-    stage_rows(a.v_cache, V, sg_v);   // (the K rows are consumed; the loads fly while the scores are mixed)
+    stage_rows(a.v_cache, V, sg_v, rows_now);   // (the K rows are consumed; the loads fly while the scores are mixed)
+    if (tid < PX_KEYS) key_row[(cur ^ 1) * PX_KEYS + tid] = row_ahead;
     // ---- scale, cap, mix over the heads, mask: a thread takes ONE (token, key) pair.  It walks the heads b in their order, reads the pair's
     //      score of head b (scale, cap) and adds its share to the mixed score of every head h, two heads per packed fp32 multiply-add with
     //      the matrix column b read four entries a load; every sum therefore runs over b upwards, as the plain kernel's does ----
