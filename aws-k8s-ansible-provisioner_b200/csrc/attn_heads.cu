@@ -997,12 +997,13 @@ __global__ void __launch_bounds__(PM_WARPS * 32) heads_attention_premix_kernel(P
 
 // ---- the same pass on warp-level tensor-core MMAs (bf16 caches, prompt portions, head sizes in multiples of 16) ----
 // One CTA of sixteen warps per 16 query tokens and ALL heads; keys go by in tiles of 32.  Per tile: the K rows of every key/value head are
-// staged (bf16) and every query head forms S = Q K^T, one 16 x 16 block per warp at a time, into an fp32 slab [heads][16][32]; the V rows
-// take the K rows' place while every thread takes one (token, key) pair, reads the pair's scores head by head (scale, cap),
-// mixes them (two heads per packed fp32 multiply-add, each head's sum in the order of the heads) and writes them back masked; then two
-// threads per (token, head) row update the row's maximum and sum and write the weights as bf16; then the warps accumulate P V into the
-// output fragments they own (unit u = head * (vdim / 16) + column block belongs to warp u mod 16), rescaled once per tile by the rows' factors.  The end goes through shared memory: division, the turn back by the query's
-// position (cosines and sines of the sixteen positions are formed once), rounding.
+// staged (bf16, asynchronous copies) and every query head forms S = Q K^T, one 16 x 16 block per warp at a time (ldmatrix + mma.sync), into
+// an fp32 slab [heads][16][32]; the V rows take the K rows' place while every thread takes one (token, key) pair, reads the pair's scores
+// head by head (scale, cap), mixes them (two heads per packed fp32 multiply-add, each head's sum in the order of the heads) and writes them
+// back masked; then two threads per (token, head) row update the row's maximum and sum and write the weights as bf16; then the warps
+// accumulate P V into the output blocks they own (unit u = head * (vdim / 16) + column block belongs to warp u mod 16), rescaled once per
+// tile by the rows' factors.  The end goes through shared memory: division, the turn back by the query's position (cosines and sines of the
+// sixteen positions are formed once), rounding.
 constexpr int PX_ROWS = 16, PX_KEYS = 32, PX_WARPS = 16, PX_THREADS = 32 * PX_WARPS, PX_SLD = 36, PX_PLD = 40;
 struct PremixMmaArgs {
   const float* q;
@@ -1038,7 +1039,7 @@ __host__ __device__ inline PremixMmaLayout premix_mma_layout(const HeadsGeom& g)
   return L;
 }
 
-// HMAX: register slots for one pair's scores (heads <= HMAX); NU: output fragments per warp (heads * vdim / 16 <= PX_WARPS * NU)
+// HMAX: register slots for one pair's mixed scores (heads <= HMAX); NU: 16 x 16 output blocks per warp (heads * vdim / 16 <= PX_WARPS * NU)
 template <int HMAX, int NU>
 __global__ void __launch_bounds__(PX_THREADS, 1) heads_attention_premix_mma_kernel(PremixMmaArgs a) {
   extern __shared__ __align__(128) unsigned char smraw[];
